@@ -37,7 +37,7 @@ class ParamSpec:
     ``dtype`` is ``"act"`` (the engine's activation dtype: bfloat16 or float32) or
     ``"float32"`` (kept in 32-bit whatever the engine dtype, e.g. router weights).
     ``init`` names the random-weights distribution: ``"matrix"`` N(0, std),
-    ``"norm"`` 1 + N(0, norm_std), ``"bias"`` N(0, bias_std).
+    ``"norm"`` 1 + N(0, norm_std), ``"bias"`` N(0, bias_std), ``"unit"`` sigmoid(N(0, 1)).
     """
     shape: tuple
     dtype: str = "act"
@@ -95,6 +95,17 @@ class AttentionSpec:
     # (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
     q_temperature: Optional[tuple] = None
     own_kv: bool = True               # False: no key/value projections; the layer attends over another's cache
+    # The fields below need prep="general", which then also rotates (``position``: split halves, no factor).
+    score_softcap: Optional[float] = None   # c: the scaled score becomes c * tanh(score / c)
+    # "zero": a key of score 0 that has no value joins the softmax: p_j = exp(s_j) / (1 + sum exp(s_j))
+    sink: Optional[str] = None
+    # the concatenated heads are multiplied by sigmoid(W_g x) before the output projection; W_g's
+    # rows follow the values' in the packed projection
+    output_gate: bool = False
+    # "first": this layer's values (of this step's tokens) are kept for the layers after it.
+    # "blend": the values become (1 - m) v + m v_first with a learned number m, before they are cached.
+    # Both kinds own the parameter ``v_mix`` (a "first" layer does not use it).
+    value_mix: Optional[str] = None
 
     @property
     def value_dim(self) -> int:
@@ -190,16 +201,28 @@ class MoESpec:
     selection_bias: bool = True       # bias added for selection only ("top_softmax": part of the logit)
     renormalize: bool = True
     routed_scale: float = 1.0
+    # "silu": silu(gate) * up.  "clamped_swiglu": g * sigmoid(activation_alpha * g) * (u + 1) with
+    # g = min(gate, activation_limit) and u = clamp(up, -activation_limit, activation_limit).
     activation: str = "silu"
+    activation_limit: float = 0.0
+    activation_alpha: float = 1.702
+    # groups > 1: the experts form that many equal groups of neighbours; a group's score is the sum of
+    # its two largest selection scores, and only experts of the keep_groups best groups can be chosen
+    groups: int = 1
+    keep_groups: int = 1
+    # a DenseMLPSpec: an expert of its own sizes that every token runs; its output is added
+    shared: Optional[Any] = None
 
 
 @dataclass(frozen=True)
 class DenseMLPSpec:
-    """A dense SwiGLU feed-forward (one always-selected expert)."""
+    """A dense gated feed-forward (one always-selected expert); activations as :class:`MoESpec`'s."""
     kind: str = "dense_mlp"
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    activation_limit: float = 0.0
+    activation_alpha: float = 1.702
 
 
 @dataclass(frozen=True)
@@ -229,6 +252,9 @@ class LayerSpec:
     # feed-forward (with its norm) may be None.
     # "post_norm": x <- norm(residual_scale * x + sublayer(x)) for each sublayer; the feed-forward
     # (with its norm) may be None
+    # "sublayer_norm": x <- x + norm(mixer(x)), x <- x + norm(ff(x)) over a 32-bit stream: the norms
+    # sit on the sublayers' outputs and the sublayers read x itself; the feed-forward (with its
+    # norm) may be None
     residual_scale: float = 1.0
     extra: dict = field(default_factory=dict)       # part name -> spec, for arrangements with more parts
     # part-local parameter name -> tuple[Source, ...]; keys are "<part>.<param>" with
@@ -268,6 +294,7 @@ class ModelSpec:
     embed_source: str = "model.embed_tokens.weight"
     head_source: Optional[str] = "lm_head.weight"   # None = tied to the embedding
     embed_scale: float = 1.0                        # the embedded tokens are multiplied by this (in the activation type)
+    logit_scale: float = 1.0                        # the logits are multiplied by this
     logit_softcap: Optional[float] = None           # c: logits become c * tanh(logits / c), in 32-bit
     ignored_prefixes: tuple = ()                    # checkpoint names skipped at load
     ignored_rule: Optional[Any] = None              # name -> bool: further names skipped at load

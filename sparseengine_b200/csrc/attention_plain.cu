@@ -6,7 +6,10 @@
 // request (window 0 = all keys); softmax state and accumulators in 32-bit; the
 // probability is rounded to the activation type before it multiplies V; the output is
 // rounded once.  The value head size `dv` may differ from the query/key size `d`: a page holds
-// the keys [kv head][slot][d] and then the values [kv head][slot][dv].  Reference: src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127,
+// the keys [kv head][slot][d] and then the values [kv head][slot][dv].
+// Options: `softcap` c > 0 caps the scaled score, s <- c tanh(s / c); `sink` adds a key of score 0
+// that has no value (one more term, exp(0), in the softmax's denominator); `gate` (with its row
+// pitch) multiplies the output element by element with sigmoid(gate[t][h * dv + i]).  Reference: src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127,
 // src/sparseengine/kernels/triton/gqa_flash_decoding_stage1.py:69-120.
 //
 // A block-table entry outside [0, num_pages) is not followed: the key is left out and a code
@@ -25,7 +28,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
                                              const int* __restrict__ seq_rows, const int* __restrict__ token_seq,
                                              const int* __restrict__ positions, T* __restrict__ out, int hq, int hkv,
                                              int d, int dv, int page_size, float scale, int window, int num_pages,
-                                             int* __restrict__ error) {
+                                             int* __restrict__ error, float softcap, int sink,
+                                             const T* __restrict__ gate, int gate_pitch) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = h / (hq / hkv);
@@ -57,6 +61,7 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
             if (dim < d) s += qr[i] * to_float(kp[dim]);
         }
         s = warp_sum(s);
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);   // m = -inf on the first key: exp(-inf) = 0
         const float p = expf(s - m_new);
@@ -79,7 +84,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
     float mt = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) mt = fmaxf(mt, sm[w]);
-    float lt = 0.f;
+    if (sink) mt = fmaxf(mt, 0.f);
+    float lt = sink ? expf(-mt) : 0.f;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) lt += sm[w] == -INFINITY ? 0.f : sl[w] * expf(sm[w] - mt);
     T* op = out + ((size_t)t * hq + h) * dv;
@@ -87,7 +93,9 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) o += sm[w] == -INFINITY ? 0.f : sacc[w][dim] * expf(sm[w] - mt);
-        op[dim] = from_float<T>(o / lt);
+        o /= lt;
+        if (gate != nullptr) o /= 1.f + expf(-to_float(gate[(size_t)t * gate_pitch + (size_t)h * dv + dim]));
+        op[dim] = from_float<T>(o);
     }
 }
 
@@ -96,14 +104,16 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
 extern "C" int se_paged_attention_plain(const void* q, const void* cache, const int* table, int table_stride,
                                         const int* seq_rows, const int* token_seq, const int* positions, void* out,
                                         int tokens, int hq, int hkv, int d, int dv, int page_size, float scale, int window,
-                                        int num_pages, int* error, int dtype, cudaStream_t stream) {
+                                        int num_pages, int* error, float softcap, int sink, const void* gate, int gate_pitch,
+                                        int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (softcap < 0.f || (gate != nullptr && gate_pitch < hq * dv)) return SE_ERR_ARGUMENT;
     if (d > 32 * se::kMaxDimPerLane || d <= 0 || dv > 32 * se::kMaxDimPerLane || dv <= 0 || hkv <= 0 || hq % hkv)
         return SE_ERR_UNSUPPORTED;
     dim3 grid(tokens, hq);
     SE_DISPATCH_DTYPE(dtype, T,
         se::paged_attention_plain_kernel<T><<<grid, 32 * se::kAttnWarps, 0, stream>>>(
             (const T*)q, (const T*)cache, table, table_stride, seq_rows, token_seq, positions, (T*)out, hq, hkv, d, dv,
-            page_size, scale, window, num_pages, error));
+            page_size, scale, window, num_pages, error, softcap, sink, (const T*)gate, gate_pitch));
     SE_LAUNCH_CHECK();
 }

@@ -27,6 +27,7 @@
 // were measured there and gained nothing) times one tile of activation rows, which the NA
 // accumulators share.
 #include "common.cuh"
+#include "glu.cuh"
 
 #include <cuda.h>
 
@@ -135,6 +136,8 @@ struct Params {
     int nt;                     // activation rows per tile: 16, 32, 64, 128 or 256
     int stages;                 // depth of the shared-memory ring
     int lists_settled;          // the tile list and offsets were complete before the kernel before this one began
+    int act_kind;               // MODE_GATE_UP: the gated activation (glu.cuh), with its limit and slope
+    float act_limit, act_alpha;
 };
 
 // ---- the persistent form ---------------------------------------------------------------------
@@ -464,7 +467,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                                 if (c0 + jj >= valid) break;
                                 const float gate = round_act<__nv_bfloat16>(__uint_as_float(g[jj]));
                                 const float up = round_act<__nv_bfloat16>(__uint_as_float(u[jj]));
-                                const float v = round_act<__nv_bfloat16>(gate / (1.f + expf(-gate))) * up;
+                                const float v = glu_value<__nv_bfloat16>(gate, up, p.act_kind, p.act_limit, p.act_alpha);
                                 p.out[(size_t)(row0 + c0 + jj) * p.n_out + n] = __float2bfloat16_rn(v);
                             }
                         }
@@ -629,9 +632,10 @@ extern "C" int se_gemm_tc_supported(int k_dim, int n_out, int nt) {
 extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, const int* sorted, const int* offsets,
                                       const int* tile_expert, const int* tile_row0, const int* num_tiles,
                                       const float* route_w, void* out, int* error, int assignments, int experts,
-                                      int max_tiles, int n_out, int k_dim, int nt, int lists_settled,
-                                      cudaStream_t stream) {
+                                      int max_tiles, int n_out, int k_dim, int nt, int lists_settled, int act_kind,
+                                      float act_limit, float act_alpha, cudaStream_t stream) {
     if (assignments <= 0 || max_tiles <= 0) return 0;
+    if (act_kind != SE_GLU_SILU && act_kind != SE_GLU_CLAMPED) return SE_ERR_ARGUMENT;
     if (!se_gemm_tc_supported(k_dim, n_out, nt) || (mode != 0 && mode != 1)) return SE_ERR_UNSUPPORTED;
     const int w_rows = mode == 0 ? 2 * n_out : n_out;
     CUtensorMap mw, mx;
@@ -641,7 +645,8 @@ extern "C" int se_moe_grouped_gemm_tc(int mode, const void* a, const void* w, co
     if (rc) return rc;
     const int na = mode == 0 ? 2 : 1;
     Params p{sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (__nv_bfloat16*)out, error,
-             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(na, nt), lists_settled ? 1 : 0};
+             n_out,  k_dim,   w_rows,      n_out,     assignments, nt, pick_stages(na, nt), lists_settled ? 1 : 0,
+             act_kind, act_limit, act_alpha};
     if (mode == 0) return launch<MODE_GATE_UP, 2>(mw, mx, p, max_tiles, stream);
     // With 128-row tiles the activation tile of the down projection is as large as a weight block
     // (K is the expert width), so two weight blocks share it, which cuts what an SM takes from L2
@@ -665,6 +670,6 @@ extern "C" int se_gemm_tc_dense(const void* x, const void* w, void* out, int* er
     rc = make_map(&mx, x, rows, k_dim, nt);
     if (rc) return rc;
     Params p{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, (__nv_bfloat16*)out, error,
-             n_out,   k_dim,   n_out,   0,       rows,    nt, pick_stages(1, nt), 1};
+             n_out,   k_dim,   n_out,   0,       rows,    nt, pick_stages(1, nt), 1, SE_GLU_SILU, 0.f, 0.f};
     return launch<MODE_DENSE, 1>(mw, mx, p, se::ceil_div(rows, nt), stream);
 }

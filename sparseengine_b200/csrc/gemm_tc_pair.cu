@@ -26,6 +26,7 @@
 // CTAs of a pair leave together.  Arithmetic and rounding points are those of gemm_tc.cu
 // (src/sparseengine/kernels/triton/moe.py:557-563,726-732,1374-1440).
 #include "common.cuh"
+#include "glu.cuh"
 
 #include <cuda.h>
 
@@ -147,6 +148,8 @@ struct Params {
     int k_dim;
     int w_rows_per_expert;      // 2I or H
     int up_offset;              // row offset of the up rows inside an expert (MODE_GATE_UP)
+    int act_kind;               // MODE_GATE_UP: the gated activation (glu.cuh), with its limit and slope
+    float act_limit, act_alpha;
 };
 
 template <int MODE>
@@ -329,9 +332,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                             const float gate = __bfloat162float(gs[j][f]);
                             const float up = __bfloat162float(us[j][f]);
                             // silu in 32-bit (fast exponential and reciprocal: the result is rounded to bfloat16 next)
-                            const float silu = __fdividef(gate, 1.f + __expf(-gate));
-                            p.out[(size_t)(row0 + c0 + j) * p.n_out + n] =
-                                __float2bfloat16_rn(round_act<__nv_bfloat16>(silu) * up);
+                            float v;
+                            if (p.act_kind == SE_GLU_SILU) {
+                                const float silu = __fdividef(gate, 1.f + __expf(-gate));
+                                v = round_act<__nv_bfloat16>(silu) * up;
+                            } else {
+                                v = glu_value<__nv_bfloat16>(gate, up, p.act_kind, p.act_limit, p.act_alpha);
+                            }
+                            p.out[(size_t)(row0 + c0 + j) * p.n_out + n] = __float2bfloat16_rn(v);
                         }
                     }
                     // a buffer is written again two chunks on, after the next chunk's barrier
@@ -479,8 +487,10 @@ extern "C" int se_moe_grouped_gemm_pair_supported(int k_dim, int n_out) {
 extern "C" int se_moe_grouped_gemm_pair(int mode, const void* a, const void* w, const int* sorted, const int* offsets,
                                         const int* tile_expert, const int* tile_row0, const int* num_tiles,
                                         const float* route_w, void* out, int* error, int assignments, int experts,
-                                        int max_tiles, int n_out, int k_dim, cudaStream_t stream) {
+                                        int max_tiles, int n_out, int k_dim, int act_kind, float act_limit,
+                                        float act_alpha, cudaStream_t stream) {
     if (assignments <= 0 || max_tiles <= 0) return 0;
+    if (act_kind != SE_GLU_SILU && act_kind != SE_GLU_CLAMPED) return SE_ERR_ARGUMENT;
     if (!se_moe_grouped_gemm_pair_supported(k_dim, n_out) || (mode != 0 && mode != 1)) return SE_ERR_UNSUPPORTED;
     const int w_rows = mode == 0 ? 2 * n_out : n_out;
     CUtensorMap mw, mx;
@@ -489,7 +499,7 @@ extern "C" int se_moe_grouped_gemm_pair(int mode, const void* a, const void* w, 
     rc = make_map(&mx, a, assignments, k_dim, kHalfN);
     if (rc) return rc;
     Params p{sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (__nv_bfloat16*)out, error,
-             n_out,  k_dim,   w_rows,      n_out};
+             n_out,  k_dim,   w_rows,      n_out, act_kind, act_limit, act_alpha};
     const int item_features = mode == 0 ? 128 : 256;
     const int max_items = max_tiles * ((n_out + item_features - 1) / item_features);
     if (mode == 0) return launch<MODE_GATE_UP>(mw, mx, p, max_items, stream);

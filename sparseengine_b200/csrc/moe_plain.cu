@@ -9,6 +9,7 @@
 // computed in 32-bit and rounded, the product with up is rounded; the down projection
 // times the routing weight (32-bit) is rounded; the sum over slots is 32-bit, rounded once.
 #include "common.cuh"
+#include "glu.cuh"
 
 namespace se {
 
@@ -210,7 +211,8 @@ __global__ void grouped_gemm_plain_kernel(const T* __restrict__ a, const T* __re
                                           const int* __restrict__ sorted, const int* __restrict__ offsets,
                                           const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                                           const int* __restrict__ num_tiles, const float* __restrict__ route_w,
-                                          T* __restrict__ out, int n_out, int k_dim, int top_k) {
+                                          T* __restrict__ out, int n_out, int k_dim, int top_k, int act_kind,
+                                          float act_limit, float act_alpha) {
     if ((int)blockIdx.x >= num_tiles[0]) return;
     const int e = tile_expert[blockIdx.x];
     const int row0 = tile_row0[blockIdx.x];
@@ -274,7 +276,7 @@ __global__ void grouped_gemm_plain_kernel(const T* __restrict__ a, const T* __re
             if (MODE == 0) {
                 const float g = round_act<T>(acc[0][i][j]);
                 const float u = round_act<T>(acc[NW - 1][i][j]);
-                v = round_act<T>(g / (1.f + expf(-g))) * u;
+                v = glu_value<T>(g, u, act_kind, act_limit, act_alpha);
             } else {
                 v = acc[0][i][j] * route_w[sorted[p]];
             }
@@ -283,19 +285,25 @@ __global__ void grouped_gemm_plain_kernel(const T* __restrict__ a, const T* __re
     }
 }
 
-// out[t, :] = cast(sum over slots (32-bit, slot order) of y[inv_pos[t * top_k + slot], :]).
+// out[t, :] = cast(sum over slots (32-bit, slot order) of y[inv_pos[t * top_k + slot], :] (+ add[t, :], last)).
 template <typename T>
-__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, T* __restrict__ out,
-                                   int hidden, int top_k) {
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, const T* __restrict__ add,
+                                   T* __restrict__ out, int hidden, int top_k) {
     grid_dependency_trigger();       // the norm that follows may fetch its weights, and the projection after it its own
     const int t = blockIdx.x;
-    if ((hidden & 7) == 0 && aligned8(y) && aligned8(out)) {
+    if ((hidden & 7) == 0 && aligned8(y) && aligned8(out) && (add == nullptr || aligned8(add))) {
         const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
         if (i >= hidden) return;
         float acc[8] = {};
         for (int k = 0; k < top_k; ++k) {
             float v[8];
             load8(y + (size_t)inv_pos[t * top_k + k] * hidden + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        if (add != nullptr) {
+            float v[8];
+            load8(add + (size_t)t * hidden + i, v);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] += v[j];
         }
@@ -306,6 +314,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
          i += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
+        if (add != nullptr) s += to_float(add[(size_t)t * hidden + i]);
         out[(size_t)t * hidden + i] = from_float<T>(s);
     }
 }
@@ -371,30 +380,33 @@ extern "C" int se_moe_plain_tile_rows() { return se::kBM; }
 
 // mode 0: gate/up + SwiGLU (a = x [tokens, k_dim], w = w13 [E, 2*n_out, k_dim]);
 // mode 1: down * routing weight (a = act [assignments, k_dim], w = w2 [E, n_out, k_dim]).
+// act_kind, act_limit, act_alpha: the gated activation of mode 0 (glu.cuh).
 extern "C" int se_moe_grouped_gemm_plain(int mode, const void* a, const void* w, const int* sorted, const int* offsets,
                                          const int* tile_expert, const int* tile_row0, const int* num_tiles,
                                          const float* route_w, void* out, int max_tiles, int n_out, int k_dim,
-                                         int top_k, int dtype, cudaStream_t stream) {
+                                         int top_k, int act_kind, float act_limit, float act_alpha, int dtype,
+                                         cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
+    if (act_kind != SE_GLU_SILU && act_kind != SE_GLU_CLAMPED) return SE_ERR_ARGUMENT;
     dim3 grid(max_tiles, se::ceil_div(n_out, se::kBN));
     SE_DISPATCH_DTYPE(dtype, T, {
         if (mode == 0)
             se::grouped_gemm_plain_kernel<T, 0><<<grid, 256, 0, stream>>>(
                 (const T*)a, (const T*)w, sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (T*)out, n_out,
-                k_dim, top_k);
+                k_dim, top_k, act_kind, act_limit, act_alpha);
         else
             se::grouped_gemm_plain_kernel<T, 1><<<grid, 256, 0, stream>>>(
                 (const T*)a, (const T*)w, sorted, offsets, tile_expert, tile_row0, num_tiles, route_w, (T*)out, n_out,
-                k_dim, top_k);
+                k_dim, top_k, act_kind, act_limit, act_alpha);
     });
     SE_LAUNCH_CHECK();
 }
 
-extern "C" int se_moe_combine(const void* y, const int* inv_pos, void* out, int tokens, int hidden, int top_k,
+extern "C" int se_moe_combine(const void* y, const int* inv_pos, const void* add, void* out, int tokens, int hidden, int top_k,
                               int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 128 * 8)), 128, 0, stream>>>((const T*)y, inv_pos, (T*)out, hidden, top_k));
+        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 128 * 8)), 128, 0, stream>>>((const T*)y, inv_pos, (const T*)add, (T*)out, hidden, top_k));
     SE_LAUNCH_CHECK();
 }
 

@@ -185,32 +185,47 @@ def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cach
 
 
 def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads,
-                          head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None):
-    """``v_head_dim``: the values' head size where it differs from the queries' and keys'."""
+                          head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
+                          sink: bool = False, gate=None):
+    """``v_head_dim``: the values' head size where it differs from the queries' and keys'.
+    ``softcap`` c: scaled scores become c tanh(s / c).  ``sink``: a key of score 0 without a value
+    joins the softmax's denominator.  ``gate``: a matrix (rows may be a view with a pitch) whose
+    sigmoid multiplies the output, [tokens, num_heads * v_head_dim]."""
     tokens = q.shape[0]
     dt = q.dtype
-    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiiii" "f" "iip" "ip")(
+    if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1 or gate.dtype != dt):
+        raise ValueError("gate must be a matrix of q's dtype with contiguous rows")
+    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiiii" "f" "iip" "fipi" "ip")(
         _ptr(q, None, "q"), _ptr(cache, dt, "cache"), _ptr(table, torch.int32, "table"), table.shape[1],
         _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, dt, "out"), tokens, num_heads, num_kv_heads,
         head_dim, int(v_head_dim or head_dim), page_size, float(scale), int(window or 0),
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
-        dtype_code(dt), _stream()), "paged_attention_plain")
+        float(softcap or 0.0), int(bool(sink)), gate.data_ptr() if gate is not None else None,
+        gate.stride(0) if gate is not None else 0, dtype_code(dt), _stream()), "paged_attention_plain")
     return out
 
 
 def qk_prep_general(proj, q_w, k_w, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads, num_kv_heads,
-                    head_dim, v_head_dim, eps, page_size, has_kv=True, temperature=None, num_pages=None):
-    """Query/key preparation without rotation: whole-projection RMS norms (optional), a query
+                    head_dim, v_head_dim, eps, page_size, has_kv=True, temperature=None, num_pages=None,
+                    inv_freq=None, rotary_dim: int = 0, v_first=None, v_mix=None):
+    """Query/key preparation in 32-bit, rounded once: whole-projection RMS norms (optional), a rotation
+    of the first ``rotary_dim`` dims of every head (split halves, angles ``position * inv_freq``), a query
     temperature ``(coef, every)`` (q times 1 + coef ln(floor((p+1)/every) + 1)), keys and values of
-    different head sizes into their page; ``has_kv=False``: the row holds queries only."""
+    different head sizes into their page; ``has_kv=False``: the row holds queries only.
+    ``v_first`` (a matrix with contiguous rows, [tokens, kv heads * v_head_dim]) and ``v_mix`` (one 32-bit
+    number on the device): the values written are ``(1 - v_mix) v + v_mix v_first``."""
     tokens = proj.shape[0]
     dt = proj.dtype
     if proj.dim() != 2 or proj.stride(1) != 1:
         raise ValueError("proj must be a matrix with contiguous rows")
     coef, every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
-    _check(_fn("se_qk_prep_general", "pipp" "ppp" "pi" "pp" "iiiii" "f" "fi" "iiip" "ip")(
+    if v_first is not None and (v_first.dim() != 2 or v_first.stride(1) != 1 or v_first.dtype != dt or v_mix is None):
+        raise ValueError("v_first must be a matrix of proj's dtype with contiguous rows, and comes with v_mix")
+    _check(_fn("se_qk_prep_general", "pipp" "pipip" "ppp" "pi" "pp" "iiiii" "f" "fi" "iiip" "ip")(
         proj.data_ptr(), proj.stride(0), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
+        _ptr(inv_freq, torch.float32, "inv_freq"), int(rotary_dim), v_first.data_ptr() if v_first is not None else None,
+        v_first.stride(0) if v_first is not None else 0, _ptr(v_mix, torch.float32, "v_mix") if v_first is not None else None,
         _ptr(positions, torch.int32, "positions"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(table, torch.int32, "table"), table.shape[1] if table is not None else 0,
         _ptr(cache, dt, "cache") if has_kv else None, _ptr(q_out, dt, "q_out"), tokens, num_heads, num_kv_heads, head_dim,
@@ -276,6 +291,19 @@ def add_rmsnorm_stream(x, y, w, eps: float, out32=None, out_act=None):
     _check(_fn("se_add_rmsnorm_stream", "ppppp" "ii" "f" "ip")(
         _ptr(x, torch.float32, "x"), _ptr(y, dt, "y"), _ptr(w, dt, "w"), _ptr(out32, torch.float32, "out32"),
         _ptr(out_act, dt, "out_act"), rows, hidden, float(eps), dtype_code(dt), _stream()), "add_rmsnorm_stream")
+
+
+def rmsnorm_add_stream(stream, y, w, eps: float, out_act=None):
+    """A stream whose sublayers are normed on their way out: ``stream += y / sqrt(mean(y^2) + eps) * w``
+    in place (32-bit); ``out_act`` receives the new stream rounded to ``y``'s type."""
+    rows, hidden = stream.shape
+    dt = y.dtype
+    if w.shape != (hidden,) or y.shape != stream.shape:
+        raise ValueError("rmsnorm_add_stream: y and w must match the stream's shape and width")
+    _check(_fn("se_rmsnorm_add_stream", "pppp" "ii" "f" "ip")(
+        _ptr(stream, torch.float32, "stream"), _ptr(y, None, "y"), _ptr(w, dt, "w"), _ptr(out_act, dt, "out_act"), rows,
+        hidden, float(eps), dtype_code(dt), _stream()), "rmsnorm_add_stream")
+    return stream
 
 
 # ---- attention over a cached latent (csrc/latent_attention.cu) -----------------------------------
@@ -522,25 +550,27 @@ SCORE_FN = {"sigmoid": 0, "softmax": 1, "top_softmax": 2}
 
 
 def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
-           logits_out=None):
+           logits_out=None, groups: int = 1, keep_groups: int = 1):
     """32-bit router logits, scores, top-k and weights.  A token's logits are summed in one
-    fixed order whatever the batch, so its experts do not depend on what shares its step."""
+    fixed order whatever the batch, so its experts do not depend on what shares its step.
+    ``groups`` > 1: the experts form that many equal groups of neighbours, a group's score is the sum of
+    its two largest selection scores, and only experts of the ``keep_groups`` best groups can be chosen."""
     tokens, hidden = x.shape
     experts = gate.shape[0]
     if gate.shape != (experts, hidden):
         raise ValueError("router weight shape does not match the activations")
     if logits_out is None:
         logits_out = torch.empty(tokens, experts, dtype=torch.float32, device=x.device)
-    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "ip")(
+    _check(_fn("se_router", "pppppp" "iiiii" "i" "f" "ii" "ip")(
         _ptr(x, None, "x"), _ptr(gate, torch.float32, "gate"), _ptr(bias, torch.float32, "bias"),
         _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"),
         _ptr(logits_out, torch.float32, "logits_out"), tokens, hidden, experts, top_k, SCORE_FN[score_fn],
-        int(renormalize), float(routed_scale), dtype_code(x.dtype), _stream()), "router")
+        int(renormalize), float(routed_scale), int(groups), int(keep_groups), dtype_code(x.dtype), _stream()), "router")
     return ids, weights
 
 
 def router_select(logits, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
-                  impl="auto"):
+                  impl="auto", groups: int = 1, keep_groups: int = 1):
     """Selection alone from given 32-bit logits [tokens, experts], or from their parts
     [chunks, tokens, terms, experts], whose sum over chunks and terms (taken in that order inside the
     kernel) is the logit.  ``impl``: "auto", "block" (a block per token, any size and score function)
@@ -549,11 +579,11 @@ def router_select(logits, bias, ids, weights, *, top_k, score_fn="sigmoid", reno
         chunks, tokens, terms, experts = logits.shape
     else:
         (tokens, experts), chunks, terms = logits.shape, 1, 1
-    _check(_fn("se_router_select", "pii" "ppp" "iiiii" "f" "ip")(
+    _check(_fn("se_router_select", "pii" "ppp" "iiiii" "f" "iii" "p")(
         _ptr(logits, torch.float32, "logits"), chunks, terms, _ptr(bias, torch.float32, "bias"),
         _ptr(ids, torch.int32, "ids"), _ptr(weights, torch.float32, "weights"), tokens, experts, top_k,
-        SCORE_FN[score_fn], int(renormalize), float(routed_scale), {"auto": 0, "block": 1, "warp": 2}[impl], _stream()),
-        "router_select")
+        SCORE_FN[score_fn], int(renormalize), float(routed_scale), {"auto": 0, "block": 1, "warp": 2}[impl], int(groups),
+        int(keep_groups), _stream()), "router_select")
     return ids, weights
 
 
@@ -596,21 +626,39 @@ def moe_max_tiles(assignments: int, experts: int, tile_rows: int) -> int:
     return -(-assignments // tile_rows) + min(experts, assignments)
 
 
-def moe_grouped_gemm_plain(mode: int, a, w, ws: dict, route_w, out, *, max_tiles, n_out, k_dim, top_k):
+# Gated activations of the experts' first product: ``silu`` is silu(gate) * up; ``clamped_swiglu`` is
+# g sigmoid(alpha g) (u + 1) with g = min(gate, limit) and u = clamp(up, -limit, limit).
+GLU_KINDS = {"silu": 0, "clamped_swiglu": 1}
+
+
+def _glu_args(activation):
+    """``activation``: a name of :data:`GLU_KINDS`, or ``(name, limit, alpha)``."""
+    if activation is None or isinstance(activation, str):
+        name, limit, alpha = activation or "silu", 0.0, 0.0
+    else:
+        name, limit, alpha = activation
+    if name not in GLU_KINDS:
+        raise ValueError(f"gated activation {name!r} is not known; known: {sorted(GLU_KINDS)}")
+    return GLU_KINDS[name], float(limit), float(alpha)
+
+
+def moe_grouped_gemm_plain(mode: int, a, w, ws: dict, route_w, out, *, max_tiles, n_out, k_dim, top_k, activation=None):
     dt = a.dtype
-    _check(_fn("se_moe_grouped_gemm_plain", "i" "ppppppppp" "iiii" "ip")(
+    _check(_fn("se_moe_grouped_gemm_plain", "i" "ppppppppp" "iiii" "iff" "ip")(
         mode, _ptr(a, None, "a"), _ptr(w, dt, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
         _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
         _ptr(route_w, torch.float32, "route_w"), _ptr(out, dt, "out"), max_tiles, n_out, k_dim, top_k,
-        dtype_code(dt), _stream()), "moe_grouped_gemm_plain")
+        *_glu_args(activation), dtype_code(dt), _stream()), "moe_grouped_gemm_plain")
     return out
 
 
-def moe_combine(y, inv_pos, out, top_k: int):
+def moe_combine(y, inv_pos, out, top_k: int, add=None):
+    """out[t] = the sum over the slots (32-bit, slot order) and, last, of ``add[t]`` ([tokens, hidden], optional:
+    a shared expert's output), rounded once."""
     tokens, hidden = out.shape
-    _check(_fn("se_moe_combine", "pppiiiip")(
-        _ptr(y, out.dtype, "y"), _ptr(inv_pos, torch.int32, "inv_pos"), _ptr(out), tokens, hidden, top_k,
-        dtype_code(out.dtype), _stream()), "moe_combine")
+    _check(_fn("se_moe_combine", "ppppiiiip")(
+        _ptr(y, out.dtype, "y"), _ptr(inv_pos, torch.int32, "inv_pos"), _ptr(add, out.dtype, "add"), _ptr(out), tokens,
+        hidden, top_k, dtype_code(out.dtype), _stream()), "moe_combine")
     return out
 
 
@@ -717,15 +765,16 @@ def moe_tile_rows_tc(assignments: int, experts: int) -> int:
 
 
 def moe_grouped_gemm_tc(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim, nt,
-                        lists_settled: bool = False):
+                        lists_settled: bool = False, activation=None):
     """``lists_settled``: the kernel launched just before this one does not write the lists in ``ws``
     (they were complete before it began).  The GEMM starts as a dependent of that kernel and then
     asks for its first weight tiles while it still runs; otherwise it waits for it first."""
-    _check(_fn("se_moe_grouped_gemm_tc", "i" "pppppppppp" "iiiiiii" "p")(
+    _check(_fn("se_moe_grouped_gemm_tc", "i" "pppppppppp" "iiiiiii" "iff" "p")(
         mode, _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
         _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
         _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(a.device)),
-        a.shape[0], experts, max_tiles, n_out, k_dim, nt, int(bool(lists_settled)), _stream()), "moe_grouped_gemm_tc")
+        a.shape[0], experts, max_tiles, n_out, k_dim, nt, int(bool(lists_settled)), *_glu_args(activation), _stream()),
+        "moe_grouped_gemm_tc")
     return out
 
 
@@ -739,14 +788,14 @@ def moe_grouped_gemm_pair_supported(k_dim: int, n_out: int) -> bool:
     return bool(f(k_dim, n_out))
 
 
-def moe_grouped_gemm_pair(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim):
+def moe_grouped_gemm_pair(mode: int, a, w, ws: dict, route_w, out, *, experts, max_tiles, n_out, k_dim, activation=None):
     """The grouped expert GEMM on pairs of SMs (``tcgen05.mma.cta_group::2``, tiles of 256 x 256); the
     tile list in ``ws`` must have been built with ``PAIR_TILE_ROWS`` rows per tile."""
-    _check(_fn("se_moe_grouped_gemm_pair", "i" "pppppppppp" "iiiii" "p")(
+    _check(_fn("se_moe_grouped_gemm_pair", "i" "pppppppppp" "iiiii" "iff" "p")(
         mode, _ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(ws["sorted"]), _ptr(ws["offsets"]),
         _ptr(ws["tile_expert"]), _ptr(ws["tile_row0"]), _ptr(ws["num_tiles"]),
         _ptr(route_w, torch.float32, "route_w"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(a.device)),
-        a.shape[0], experts, max_tiles, n_out, k_dim, _stream()), "moe_grouped_gemm_pair")
+        a.shape[0], experts, max_tiles, n_out, k_dim, *_glu_args(activation), _stream()), "moe_grouped_gemm_pair")
     return out
 
 

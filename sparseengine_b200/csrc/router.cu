@@ -347,10 +347,12 @@ __device__ __forceinline__ float logit_at(const LogitParts& s, int t, int e) {
 }
 
 // One block per token: score function, selection bias, top-k in the reference's order,
-// renormalisation.
+// renormalisation.  With `groups` > 1 the experts form that many equal groups of neighbours; a
+// group's score is the sum of its two largest selection scores (of its one, if it has one), and
+// only experts of the `keep_groups` best groups (score descending, index ascending) can be chosen.
 __global__ void router_select_kernel(const LogitParts src, const float* __restrict__ bias,
                                      int* __restrict__ ids, float* __restrict__ weights, int experts, int top_k,
-                                     int score_fn, int renormalize, float routed_scale) {
+                                     int score_fn, int renormalize, float routed_scale, int groups, int keep_groups) {
     extern __shared__ __align__(16) float sel[];
     const int padded = (experts + 3) & ~3;
     float* pj = sel;                     // [experts] probabilities
@@ -400,6 +402,27 @@ __global__ void router_select_kernel(const LogitParts src, const float* __restri
         }
     }
     __syncthreads();
+    if (groups > 1) {
+        float* gscore = (float*)(ranks);          // [groups], overwritten by the ranks below
+        const int per = experts / groups;
+        for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+            float a = -INFINITY, b = -INFINITY;   // largest, second largest
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = sj[e];
+                if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+            }
+            gscore[g] = per > 1 ? a + b : a;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+            const int g = e / per;
+            const float gs = gscore[g];
+            int before = 0;
+            for (int o = 0; o < groups; ++o) before += (gscore[o] > gs) || (gscore[o] == gs && o < g);
+            if (before >= keep_groups) sj[e] = -INFINITY;      // the groups' scores are complete: nobody reads sj for them now
+        }
+        __syncthreads();
+    }
     // rank of e = number of experts that precede it in (score descending, index ascending);
     // ranks are a permutation, the chosen are the ranks below top_k and the threshold is
     // the score of rank top_k-1.
@@ -578,10 +601,13 @@ router_select_warp_kernel(const LogitParts src, const float* __restrict__ bias, 
 // impl: 0 = by sizes, 1 = the block-per-token kernel, 2 = the warp-per-token kernel
 static int launch_select(const float* logits, int chunks, int terms, const float* bias, int* ids, float* weights,
                          int tokens, int experts, int top_k, int score_fn, int renormalize, float routed_scale, int impl,
-                         cudaStream_t stream) {
+                         int groups, int keep_groups, cudaStream_t stream) {
     const se::LogitParts src{logits, tokens, experts, chunks, terms};
     const size_t smem_sel = (size_t)((experts + 3) & ~3) * 4 * sizeof(float);
-    const bool warp_ok = score_fn == 0 && experts <= 32 * se::kSelPer && top_k <= 256;
+    if (groups < 1) groups = 1;
+    if (groups > 1 && (experts % groups || keep_groups < 1 || keep_groups > groups ||
+                       (long long)keep_groups * (experts / groups) < top_k)) return SE_ERR_ARGUMENT;
+    const bool warp_ok = score_fn == 0 && experts <= 32 * se::kSelPer && top_k <= 256 && groups == 1;
     if (impl == 2 && !warp_ok) return SE_ERR_UNSUPPORTED;
     if (experts > 200 * 1024 / 16) return SE_ERR_UNSUPPORTED;
     // A warp's selection is one long chain of dependent steps (8 us for a token, against 6.6 us
@@ -596,7 +622,7 @@ static int launch_select(const float* logits, int chunks, int terms, const float
         if (e != cudaSuccess) return (int)e;
     }
     se::router_select_kernel<<<tokens, 256, smem_sel, stream>>>(src, bias, ids, weights, experts, top_k, score_fn,
-                                                                renormalize, routed_scale);
+                                                                renormalize, routed_scale, groups, keep_groups);
     SE_LAUNCH_CHECK();
 }
 
@@ -604,11 +630,11 @@ static int launch_select(const float* logits, int chunks, int terms, const float
 // experts] whose sum over chunks and terms (in that order) is the logit.
 extern "C" int se_router_select(const float* logits, int chunks, int terms, const float* bias, int* ids, float* weights,
                                 int tokens, int experts, int top_k, int score_fn, int renormalize, float routed_scale,
-                                int impl, cudaStream_t stream) {
+                                int impl, int groups, int keep_groups, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (top_k <= 0 || top_k > experts || impl < 0 || impl > 2 || chunks < 1 || terms < 1) return SE_ERR_ARGUMENT;
     return launch_select(logits, chunks, terms, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize,
-                         routed_scale, impl, stream);
+                         routed_scale, impl, groups, keep_groups, stream);
 }
 
 // Most experts the selection takes (four floats per expert in 200 KB of shared memory), and the
@@ -619,7 +645,8 @@ extern "C" int se_router_max_unaligned_width() { return 200 * 1024 / (se::kRoute
 // logits: float [tokens, experts] workspace (also the logits output for whoever wants them).
 extern "C" int se_router(const void* x, const float* gate, const float* bias, int* ids, float* weights,
                          float* logits, int tokens, int hidden, int experts, int top_k, int score_fn,
-                         int renormalize, float routed_scale, int dtype, cudaStream_t stream) {
+                         int renormalize, float routed_scale, int groups, int keep_groups, int dtype,
+                         cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (top_k <= 0 || top_k > experts || logits == nullptr) return SE_ERR_ARGUMENT;
     const int tile_tokens = tokens < se::kRouterTokens ? tokens : se::kRouterTokens;
@@ -662,5 +689,5 @@ extern "C" int se_router(const void* x, const float* gate, const float* bias, in
         }
     });
     return launch_select(logits, 1, 1, bias, ids, weights, tokens, experts, top_k, score_fn, renormalize, routed_scale, 0,
-                         stream);
+                         groups, keep_groups, stream);
 }

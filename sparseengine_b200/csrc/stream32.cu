@@ -146,6 +146,55 @@ __global__ void add_rmsnorm_stream_kernel(const float* x, const T* y, const T* _
     }
 }
 
+// One block per row of a 32-bit stream whose sublayers are normed on their way out:
+// stream += y / sqrt(mean(y^2) + eps) * w (32-bit), and out_act (optional) receives the new stream
+// rounded to the activation type, which is what the next sublayer reads.
+template <typename T>
+__global__ void rmsnorm_add_stream_kernel(float* stream, const T* y, const T* __restrict__ w, T* out_act, int hidden,
+                                          float eps) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[33];
+    grid_dependency_trigger();
+    grid_dependency_wait();
+    const size_t base = (size_t)blockIdx.x * hidden;
+    const bool vec = (hidden & 7) == 0 && aligned8(stream) && aligned8(y) && aligned8(w) &&
+                     (out_act == nullptr || aligned8(out_act));
+    float ss = 0.f;
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float v[8];
+            load8(y + base + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { row[i + j] = v[j]; ss += v[j] * v[j]; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = to_float(y[base + i]);
+            row[i] = v;
+            ss += v * v;
+        }
+    }
+    // every thread reads back the elements of the row that it wrote itself
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float wv[8], x[8];
+            load8(w + i, wv);
+            load8(stream + base + i, x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] += row[i + j] * inv * wv[j];
+            store8(stream + base + i, x);
+            if (out_act != nullptr) store8(out_act + base + i, x);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float x = stream[base + i] + row[i] * inv * to_float(w[i]);
+            stream[base + i] = x;
+            if (out_act != nullptr) out_act[base + i] = from_float<T>(x);
+        }
+    }
+}
+
 __device__ __forceinline__ float act_apply(float v, int kind) {
     if (kind == 0) { const float r = fmaxf(v, 0.f); return r * r; }                       // squared relu
     if (kind == 1) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));   // gelu (tanh form)
@@ -232,6 +281,25 @@ extern "C" int se_add_rmsnorm_stream(const float* x, const void* y, const void* 
         }
         se::add_rmsnorm_stream_kernel<T><<<rows, threads, smem, stream>>>(x, (const T*)y, (const T*)w, out32, (T*)out_act,
                                                                           hidden, eps);
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_rmsnorm_add_stream(float* stream_, const void* y, const void* w, void* out_act, int rows, int hidden,
+                                     float eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden > se_layernorm_max_width()) return SE_ERR_UNSUPPORTED;
+    if (y == nullptr || w == nullptr) return SE_ERR_ARGUMENT;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    const int threads = hidden >= 8192 ? 512 : hidden >= 1024 ? 256 : 128;
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(se::rmsnorm_add_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        cudaError_t e = SE_LAUNCH_DEPENDENT("norm", se::rmsnorm_add_stream_kernel<T>, dim3(rows), dim3(threads), smem, stream,
+                                             stream_, (const T*)y, (const T*)w, (T*)out_act, hidden, eps);
+        if (e != cudaSuccess) return (int)e;
     });
     SE_LAUNCH_CHECK();
 }

@@ -16,8 +16,9 @@ import torch
 from ..config.specs import ModelSpec, ParamSpec, Source
 from ..csrc import ops
 from ..parts.base import KVRequest, StateRequest, StepContext, make_norm
-from ..parts.block import PostNormBlock, PreNormBlock, PreNormStreamBlock, make_block
+from ..parts.block import PostNormBlock, PreNormBlock, PreNormStreamBlock, SublayerNormBlock, make_block
 from ..parts.linear import linear, linear32
+from ..parts.norm import RMSNorm
 
 
 @dataclass
@@ -172,6 +173,13 @@ class Model:
                 y = timed("feed_forward", block.feed_forward.forward, hidden, step) if block.feed_forward is not None else None
                 hidden, residual = timed("feed_forward_norm", block.feed_forward_norm.forward_stream, residual, y, block.alpha)
             return hidden, residual
+        if isinstance(block, SublayerNormBlock):
+            y = timed("mixer." + block.mixer.spec.kind, block.mixer.forward, hidden, step, slot)
+            hidden, residual = timed("mixer_norm", block.mixer_norm.forward_into_stream, residual, y)
+            if block.feed_forward is not None:
+                y = timed("feed_forward." + block.feed_forward.spec.kind, block.feed_forward.forward, hidden, step)
+                hidden, residual = timed("feed_forward_norm", block.feed_forward_norm.forward_into_stream, residual, y)
+            return hidden, residual
         if isinstance(block, PreNormStreamBlock):
             x, residual = timed("mixer_norm", block.mixer_norm.forward_stream, residual, hidden)
             hidden = timed("mixer." + block.mixer.spec.kind, block.mixer.forward, x, step, slot)
@@ -248,7 +256,8 @@ class Model:
         elif stream32:      # the final norm reads the wanted rows of the stream
             r = torch.empty(n, s.hidden_size, dtype=torch.float32, device=hidden.device)
             ops.gather_rows(residual, want_rows, r)
-            h, _ = self.final_norm.forward(r)
+            # a norm that reads the 32-bit stream and answers in the activation type
+            h, _ = self.final_norm.forward_stream(r) if isinstance(self.final_norm, RMSNorm) else self.final_norm.forward(r)
         else:
             h = torch.empty(n, s.hidden_size, dtype=self.dtype, device=hidden.device)
             ops.gather_rows(hidden, want_rows, h)
@@ -259,6 +268,8 @@ class Model:
             else:
                 h, _ = self.final_norm.forward(h)
         logits = linear(h, self.head)
+        if s.logit_scale != 1.0:
+            logits.mul_(float(s.logit_scale))
         if s.logit_softcap is not None:
             ops.softcap_(logits, float(s.logit_softcap))
         return logits

@@ -4,6 +4,13 @@ qkv projection → (optional) whole-projection QK RMSNorm → position encoding 
 their page → attention over the request's pages → output projection.  Order of effects
 as in the reference (src/sparseengine/models/minimax_m2.py:334-359): this step's keys are
 written before attention reads the cache.
+
+The general preparation (``prep="general"``) adds, each by a field of the spec: values of a head
+size of their own, a query temperature, layers without keys of their own, a cap on the scores,
+a sink of score 0 in the softmax, an output gate, and values blended with those of an earlier
+layer.  The blended values are what is cached; the earlier layer's values of this step's tokens
+travel from layer to layer in the step's scratch (``StepContext.extras``), so nothing of them
+is kept between steps.
 """
 from __future__ import annotations
 
@@ -35,12 +42,14 @@ class PagedAttention(Mixer):
                     and 0 < s.value_dim <= ops.LIMITS["attention_max_head_dim"]):
                 raise ValueError(f"head sizes {s.head_dim} / {s.value_dim} are not supported (1 to "
                                  f"{ops.LIMITS['attention_max_head_dim']})")
-            if s.position is not None:
-                raise ValueError("the general preparation has no rotation; leave position unset")
+            if s.position is not None and getattr(s.position, "pairing", "split_half") != "split_half":
+                raise ValueError("the general preparation rotates split halves only")
             if s.q_temperature is not None and not (len(s.q_temperature) == 2 and int(s.q_temperature[1]) > 0):
                 raise ValueError("q_temperature is (coef, every) with every > 0")
-        elif s.v_head_dim not in (None, s.head_dim) or s.q_temperature is not None or not s.own_kv:
-            raise ValueError("v_head_dim, q_temperature and own_kv=False need prep='general'")
+        elif (s.v_head_dim not in (None, s.head_dim) or s.q_temperature is not None or not s.own_kv
+              or s.score_softcap is not None or s.sink is not None or s.output_gate or s.value_mix is not None):
+            raise ValueError("v_head_dim, q_temperature, own_kv=False, score_softcap, sink, output_gate and value_mix "
+                             "need prep='general'")
         elif s.head_dim <= 0 or s.head_dim % 16 or s.head_dim > ops.LIMITS["attention_max_head_dim"]:
             raise ValueError(f"head_dim {s.head_dim} is not supported (multiples of 16 up to "
                              f"{ops.LIMITS['attention_max_head_dim']})")
@@ -51,17 +60,29 @@ class PagedAttention(Mixer):
             raise ValueError(f"qk_norm {s.qk_norm!r} is not supported")
         if s.window is not None and s.window <= 0:
             raise ValueError("window must be positive (None: all keys)")
+        if s.score_softcap is not None and not s.score_softcap > 0:
+            raise ValueError("score_softcap must be positive (None: no cap)")
+        if s.sink not in (None, "zero"):
+            raise ValueError(f"sink {s.sink!r} is not known (None or 'zero')")
+        if s.value_mix not in (None, "first", "blend"):
+            raise ValueError(f"value_mix {s.value_mix!r} is not known (None, 'first' or 'blend')")
+        if s.value_mix is not None and not s.own_kv:
+            raise ValueError("value_mix needs values of the layer's own")
         self.position = make_position(s.position, dtype) if s.position is not None else None
         rot = getattr(s.position, "rotary_dim", 0) if s.position is not None else 0
         if rot > s.head_dim:
             raise ValueError(f"the position encoding rotates {rot} dims, a head has {s.head_dim}")
-        self.q_norm = self.k_norm = None
+        self.q_norm = self.k_norm = self.v_mix = None
 
     def parameters(self):
         s = self.spec
         q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         rows = q + (kv + s.num_kv_heads * s.value_dim if s.own_kv else 0)
+        if s.output_gate:
+            rows += s.num_heads * s.value_dim
         out = {"qkv": ParamSpec((rows, s.hidden_size)), "o": ParamSpec((s.hidden_size, s.num_heads * s.value_dim))}
+        if s.value_mix is not None:
+            out["v_mix"] = ParamSpec((), "float32", "unit")
         if s.qk_norm is not None:
             out["q_norm"] = ParamSpec((q,), "act", "norm")
             if s.own_kv:
@@ -72,20 +93,43 @@ class PagedAttention(Mixer):
         s = self.spec
         return KVRequest(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim)
 
+    VALUE_MIX_KEY = "attention.value_mix.first"     # in StepContext.extras: the kept values [tokens, kv heads * value_dim]
+
     def forward_general(self, x, step, slot):
-        """No rotation: whole-projection norms, query temperature and the page writes in one kernel
-        (32-bit, rounded once); a layer without keys of its own only prepares its queries."""
+        """Whole-projection norms, rotation, query temperature, value blending and the page writes in
+        one kernel (32-bit, rounded once); a layer without keys of its own only prepares its queries."""
         s = self.spec
         tokens = x.shape[0]
         proj = linear(x, self.qkv)
-        q = torch.empty(tokens, s.num_heads * s.head_dim, dtype=x.dtype, device=x.device)
+        q_cols, kv_cols = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        v_cols = s.num_kv_heads * s.value_dim
+        inv_freq, rotary_dim = None, 0
+        if self.position is not None:
+            rope = as_rotary_args(self.position.kernel_args(x.device))
+            if rope.scale != 1.0 or rope.pairing != "split_half":
+                raise ValueError("the general preparation rotates split halves without a factor on cos and sin")
+            inv_freq, rotary_dim = rope.inv_freq, rope.rotary_dim
+        v_first = None
+        if s.value_mix is not None:
+            kept = step.extras.get(self.VALUE_MIX_KEY)
+            if s.value_mix == "first" or kept is None:
+                # the view keeps the projection alive for the layers that follow in this step
+                step.extras[self.VALUE_MIX_KEY] = proj[:, q_cols + kv_cols:q_cols + kv_cols + v_cols]
+            else:
+                v_first = kept
+        q = torch.empty(tokens, q_cols, dtype=x.dtype, device=x.device)
         writes = s.own_kv and slot.write_cache
         ops.qk_prep_general(proj, self.q_norm, self.k_norm if s.own_kv else None, step.positions, step.token_seq,
                             step.seq_rows, slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
                             head_dim=s.head_dim, v_head_dim=s.value_dim, eps=s.qk_norm_eps, page_size=slot.page_size,
-                            has_kv=writes, temperature=s.q_temperature)
+                            has_kv=writes, temperature=s.q_temperature, inv_freq=inv_freq, rotary_dim=rotary_dim,
+                            v_first=v_first, v_mix=self.v_mix if v_first is not None else None)
         attn = torch.empty(tokens, s.num_heads * s.value_dim, dtype=x.dtype, device=x.device)
-        self.attend(q, attn, step, slot)
+        gate = None
+        if s.output_gate:
+            g0 = q_cols + (kv_cols + v_cols if s.own_kv else 0)
+            gate = proj[:, g0:g0 + s.num_heads * s.value_dim]
+        self.attend(q, attn, step, slot, gate=gate)
         return linear(attn, self.o)
 
     def forward(self, x, step, slot):
@@ -129,11 +173,14 @@ class PagedAttention(Mixer):
                 and step.num_tokens >= self.portion_min_average * step.num_seqs)
     use_tensor_cores = None      # False: always the plain kernel
 
-    def attend(self, q, out, step, slot, after_qk_prep=False):
+    def attend(self, q, out, step, slot, after_qk_prep=False, gate=None):
         """``after_qk_prep``: the kernel launched last is the one that wrote this step's keys and
-        ``q``; the split-key kernel then looks its place in the block table up while it still runs."""
+        ``q``; the split-key kernel then looks its place in the block table up while it still runs.
+        ``gate``: the output gate's projection (a view with a row pitch), or None."""
         s = self.spec
+        variant = s.score_softcap is not None or s.sink is not None or gate is not None
         if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16 and s.value_dim == s.head_dim
+                and not variant
                 and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)):
             if not self.takes_portion_kernel(step):
                 max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
@@ -151,7 +198,8 @@ class PagedAttention(Mixer):
             return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
-                                  page_size=slot.page_size, scale=s.scale, window=s.window, v_head_dim=s.value_dim)
+                                  page_size=slot.page_size, scale=s.scale, window=s.window, v_head_dim=s.value_dim,
+                                  softcap=s.score_softcap, sink=s.sink == "zero", gate=gate)
 
 
 register_mixer("attention", PagedAttention)

@@ -10,8 +10,8 @@ the one that may ask for pages or state), ``forward(hidden, residual, step, slot
 ``(hidden, residual)``, and an attribute ``mixer``.  Parts beyond the four of ``pre_norm`` come
 from ``LayerSpec.extra``.
 
-``post_norm`` (:class:`PostNormBlock`) and ``pre_norm_stream`` (:class:`PreNormStreamBlock`) are the
-arrangements over a 32-bit stream.
+``post_norm`` (:class:`PostNormBlock`), ``pre_norm_stream`` (:class:`PreNormStreamBlock`) and
+``sublayer_norm`` (:class:`SublayerNormBlock`) are the arrangements over a 32-bit stream.
 """
 from __future__ import annotations
 
@@ -114,7 +114,43 @@ class PreNormStreamBlock:
         return pending, stream
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "post_norm": PostNormBlock, "pre_norm_stream": PreNormStreamBlock}
+class SublayerNormBlock:
+    """Norm on each sublayer's output, over a 32-bit stream: ``x <- x + norm(mixer(x))``, then (if the
+    layer has a feed-forward) ``x <- x + norm(feed_forward(x))``.  The sublayers read ``x`` itself.  The
+    block carries ``(x in the activation type, x in 32-bit)`` like :class:`PostNormBlock`
+    (``ModelSpec.residual_stream = "float32"``); norm, add and the rounded copy are one kernel.  The norms
+    are parts with ``forward_into_stream(stream, y)`` (``parts.norm.RMSNorm``)."""
+
+    def __init__(self, spec, dtype):
+        self.spec = spec
+        self.mixer = make_mixer(spec.mixer, dtype)
+        self.mixer_norm = make_norm(spec.mixer_norm, dtype)
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make_feed_forward(spec.feed_forward, dtype)
+            self.feed_forward_norm = make_norm(spec.feed_forward_norm, dtype)
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not hasattr(n, "forward_into_stream"):
+                raise ValueError("a block with norms on the sublayers' outputs needs norms with forward_into_stream")
+
+    def parts(self) -> dict:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            out["feed_forward"] = self.feed_forward
+            out["feed_forward_norm"] = self.feed_forward_norm
+        return out
+
+    def forward(self, hidden, stream, step, slot):
+        y = self.mixer.forward(hidden, step, slot)
+        hidden, stream = self.mixer_norm.forward_into_stream(stream, y)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(hidden, step)
+            hidden, stream = self.feed_forward_norm.forward_into_stream(stream, y)
+        return hidden, stream
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "post_norm": PostNormBlock, "pre_norm_stream": PreNormStreamBlock,
+                "sublayer_norm": SublayerNormBlock}
 
 
 def make_block(spec, dtype):

@@ -26,6 +26,20 @@ class _RoutedSwiGLU(FeedForward):
     hidden: int
     inter: int
 
+    # the gated activation of the first product: a name of ops.GLU_KINDS, or (name, limit, alpha)
+    activation_args = None
+
+    @staticmethod
+    def activation_of(spec):
+        """The kernels' activation argument from a spec's ``activation*`` fields (checked)."""
+        if spec.activation not in ops.GLU_KINDS:
+            raise ValueError(f"activation {spec.activation!r} is not supported; known: {sorted(ops.GLU_KINDS)}")
+        if spec.activation == "silu":
+            return None
+        if not spec.activation_limit > 0:
+            raise ValueError(f"activation {spec.activation!r} needs a positive activation_limit")
+        return (spec.activation, float(spec.activation_limit), float(spec.activation_alpha))
+
     # None: tensor cores whenever the sizes allow (bfloat16, row pitches that TMA takes);
     # False: always the CUDA-core kernels (the float32 path uses them in any case).
     use_tensor_cores = None
@@ -73,7 +87,8 @@ class _RoutedSwiGLU(FeedForward):
     # many experts' weights a step had to read.
     route_stats = None
 
-    def run_experts(self, x, ids, weights):
+    def run_experts(self, x, ids, weights, add=None):
+        """``add``: a [tokens, hidden] tensor that joins the 32-bit sum over the slots before it is rounded."""
         tokens = x.shape[0]
         a = tokens * self.top_k
         dev = x.device
@@ -102,30 +117,42 @@ class _RoutedSwiGLU(FeedForward):
         y = torch.empty(a, self.hidden, dtype=x.dtype, device=dev)
         if pair:
             ops.moe_grouped_gemm_pair(0, xs, self.w13, ws, None, act, experts=self.num_experts, max_tiles=max_tiles,
-                                      n_out=self.inter, k_dim=self.hidden)
+                                      n_out=self.inter, k_dim=self.hidden, activation=self.activation_args)
             ops.moe_grouped_gemm_pair(1, act, self.w2, ws, weights, y, experts=self.num_experts, max_tiles=max_tiles,
                                       n_out=self.hidden, k_dim=self.inter)
         elif tc:
             # the second product starts while the first still runs: the lists are older than both
             ops.moe_grouped_gemm_tc(0, xs, self.w13, ws, None, act, experts=self.num_experts, max_tiles=max_tiles,
-                                    n_out=self.inter, k_dim=self.hidden, nt=tile_rows, lists_settled=settled)
+                                    n_out=self.inter, k_dim=self.hidden, nt=tile_rows, lists_settled=settled,
+                                    activation=self.activation_args)
             ops.moe_grouped_gemm_tc(1, act, self.w2, ws, weights, y, experts=self.num_experts, max_tiles=max_tiles,
                                     n_out=self.hidden, k_dim=self.inter, nt=tile_rows, lists_settled=True)
         else:
             ops.moe_grouped_gemm_plain(0, x, self.w13, ws, None, act, max_tiles=max_tiles, n_out=self.inter,
-                                       k_dim=self.hidden, top_k=self.top_k)
+                                       k_dim=self.hidden, top_k=self.top_k, activation=self.activation_args)
             ops.moe_grouped_gemm_plain(1, act, self.w2, ws, weights, y, max_tiles=max_tiles, n_out=self.hidden,
                                        k_dim=self.inter, top_k=self.top_k)
         out = torch.empty(tokens, self.hidden, dtype=x.dtype, device=dev)
-        ops.moe_combine(y, ws["inv_pos"], out, self.top_k)
+        ops.moe_combine(y, ws["inv_pos"], out, self.top_k, add=add)
         return out
 
 
 class SparseMoE(_RoutedSwiGLU):
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not supported (only 'silu')")
+        self.activation_args = self.activation_of(spec)
+        if spec.groups < 1 or (spec.groups > 1 and (
+                spec.num_experts % spec.groups or not 1 <= spec.keep_groups <= spec.groups
+                or spec.keep_groups * (spec.num_experts // spec.groups) < spec.top_k)):
+            raise ValueError(f"{spec.num_experts} experts do not form {spec.groups} equal groups of which "
+                             f"{spec.keep_groups} can hold the {spec.top_k} chosen")
+        if spec.groups > 1 and spec.score_fn == "top_softmax":
+            raise ValueError("grouped selection goes by scores; 'top_softmax' has none")
+        self.shared = None
+        if spec.shared is not None:
+            if spec.shared.hidden_size != spec.hidden_size:
+                raise ValueError("the shared expert must have the routed experts' width")
+            self.shared = DenseMLP(spec.shared, dtype)
         if spec.score_fn not in ops.SCORE_FN:
             raise ValueError(f"score function {spec.score_fn!r} is not supported")
         if not 0 < spec.top_k <= spec.num_experts:
@@ -144,7 +171,10 @@ class SparseMoE(_RoutedSwiGLU):
         self.selection_bias = None
 
     def bind(self, tensors):
-        super().bind(tensors)
+        mine = {k: v for k, v in tensors.items() if not k.startswith("shared_")}
+        super().bind(mine)
+        if self.shared is not None:
+            self.shared.bind({k[len("shared_"):]: v for k, v in tensors.items() if k.startswith("shared_")})
         self._gate_split = None          # derived from the gate
 
     def parameters(self):
@@ -154,6 +184,9 @@ class SparseMoE(_RoutedSwiGLU):
                "w2": ParamSpec((s.num_experts, s.hidden_size, s.intermediate_size))}
         if s.selection_bias:
             out["selection_bias"] = ParamSpec((s.num_experts,), "float32", "bias")
+        if self.shared is not None:
+            for name, p in self.shared.parameters().items():
+                out["shared_" + name] = p
         return out
 
     # Debugging aid: set to a list and every call appends the chosen expert ids (a CPU
@@ -207,10 +240,10 @@ class SparseMoE(_RoutedSwiGLU):
             # the selection adds the parts itself (chunk by chunk, term by term)
             ops.router_select(parts.view(chunks, tokens, 3, self.num_experts), self.selection_bias, ids, weights,
                               top_k=self.top_k, score_fn=s.score_fn, renormalize=s.renormalize,
-                              routed_scale=s.routed_scale)
+                              routed_scale=s.routed_scale, groups=s.groups, keep_groups=s.keep_groups)
         else:
             ops.router(x, self.gate, self.selection_bias, ids, weights, top_k=self.top_k, score_fn=s.score_fn,
-                       renormalize=s.renormalize, routed_scale=s.routed_scale)
+                       renormalize=s.renormalize, routed_scale=s.routed_scale, groups=s.groups, keep_groups=s.keep_groups)
         if self.capture is not None:
             self.capture.append(ids.cpu())
         return ids, weights
@@ -219,16 +252,17 @@ class SparseMoE(_RoutedSwiGLU):
     # src/sparseengine/models/minimax_m2.py:254-268); the engine sets it from its options.
     chunk_rows = 16384
 
+    def forward_rows(self, x, step):
+        # the shared expert first: the kernel that sums the routed slots adds its output
+        shared = self.shared.forward(x, step) if self.shared is not None else None
+        ids, weights = self.route(x)
+        return self.run_experts(x, ids, weights, add=shared)
+
     def forward(self, x, step):
         if x.shape[0] <= self.chunk_rows:
-            ids, weights = self.route(x)
-            return self.run_experts(x, ids, weights)
-        outs = []
-        for a in range(0, x.shape[0], self.chunk_rows):
-            xc = x[a:a + self.chunk_rows]
-            ids, weights = self.route(xc)
-            outs.append(self.run_experts(xc, ids, weights))
-        return torch.cat(outs, 0)
+            return self.forward_rows(x, step)
+        return torch.cat([self.forward_rows(x[a:a + self.chunk_rows], step)
+                          for a in range(0, x.shape[0], self.chunk_rows)], 0)
 
 
 class DenseMLP(_RoutedSwiGLU):
@@ -236,8 +270,9 @@ class DenseMLP(_RoutedSwiGLU):
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not supported (only 'silu')")
+        self.activation_args = self.activation_of(spec)
+        if spec.hidden_size <= 0 or spec.intermediate_size <= 0:
+            raise ValueError("hidden_size and intermediate_size must be positive")
         self.num_experts, self.top_k = 1, 1
         self.hidden, self.inter = spec.hidden_size, spec.intermediate_size
 

@@ -42,6 +42,17 @@ class RMSNorm(Norm):
         ops.add_rmsnorm_stream(stream, y, self.weight, self.spec.eps, out32=stream if y is not None else None, out_act=out)
         return out, stream
 
+    def forward_into_stream(self, stream, y):
+        """A norm on a sublayer's output (kernel: csrc/stream32.cu): ``stream += norm(y)`` in place
+        (32-bit).  Returns ``(the new stream in the activation type, stream)``; in a 32-bit engine the
+        first is the stream itself."""
+        if self.dtype == torch.float32:
+            ops.rmsnorm_add_stream(stream, y, self.weight, self.spec.eps)
+            return stream, stream
+        out = torch.empty(stream.shape, dtype=self.dtype, device=stream.device)
+        ops.rmsnorm_add_stream(stream, y, self.weight, self.spec.eps, out_act=out)
+        return out, stream
+
 
 register_norm("rms", RMSNorm)
 

@@ -77,10 +77,12 @@ def scaled_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]) -
         raise ValueError(f"frequency scaling {kind!r} is not supported (linear, llama3 and yarn are; "
                          "types that depend on the sequence length are not)")
     factor = _need(scaling, "factor", kind)
+    if kind == "linear":
+        if not factor > 0:
+            raise ValueError(f"linear frequency scaling: factor must be positive, got {factor}")
+        return inv / factor, 1.0
     if factor < 1.0:
         raise ValueError(f"{kind} frequency scaling: factor must be at least 1, got {factor}")
-    if kind == "linear":
-        return inv / factor, 1.0
     original = _need(scaling, "original_max_position_embeddings", kind)
     if original <= 0:
         raise ValueError(f"{kind} frequency scaling: original_max_position_embeddings must be positive")

@@ -3,7 +3,8 @@ configuration and a seed, or fill a built model in place on its device.
 
 Each checkpoint tensor draws from a generator seeded by (seed, tensor name), so a
 folder can be produced tensor by tensor and any subset reproduces.  Distributions:
-matrices N(0, std); norm weights 1 + N(0, norm_std); selection bias N(0, bias_std).
+matrices N(0, std); norm weights 1 + N(0, norm_std); selection bias N(0, bias_std); blending
+weights ("unit") sigmoid(N(0, 1)).
 The reference's counterpart is its tiny-random debug mode
 (src/sparseengine/debug/tiny_random.py:255-292: every float parameter N(0, 0.02) from one
 seeded generator).
@@ -36,6 +37,8 @@ def _draw(shape, init: str, seed: int, name: str, device, std, norm_std, bias_st
         return 1.0 + x * norm_std
     if init == "bias":
         return x * bias_std
+    if init == "unit":
+        return torch.sigmoid(x)
     return x * std
 
 
@@ -90,6 +93,8 @@ def init_random_(model: Model, seed: int, device, *, std: float = 0.02, norm_std
                 x = 1.0 + x * norm_std
             elif p.spec.init == "bias":
                 x = x * bias_std
+            elif p.spec.init == "unit":
+                x = torch.sigmoid(x)
             else:
                 x = x * std
             flat[start:start + n].copy_(x)
