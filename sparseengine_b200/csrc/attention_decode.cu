@@ -11,11 +11,16 @@
 // src/sparseengine/kernels/triton/flash_decoding_stage2.py:27-45): scores and softmax in
 // 32-bit, probabilities rounded to bfloat16 before they multiply V, the output rounded once.
 //
-// Any page size; head sizes 64 and 128 (others use the plain kernel); a window is honoured.
+// Any page size; query/key head sizes 64 and 128, value head sizes 32, 64 and 128 (others use the
+// plain kernel); a window is honoured.  A page holds the keys [kv head][slot][D] and then the values
+// [kv head][slot][DV].  The softmax's options (a cap on the scores, a sink of score 0, an output gate)
+// are those of mma_util.cuh's SoftmaxOptions; the sink joins once, where the last sum is taken (here
+// for one split, in the second kernel for several), and the gate where the output is rounded.
 // A block-table entry outside [0, num_pages) is not followed: the rows it stands for are
 // zero-filled and a code goes to the error word.
 #include "common.cuh"
 #include "mma_util.cuh"
+#include <type_traits>
 
 namespace se {
 namespace dec {
@@ -27,16 +32,16 @@ constexpr int kThreads = 32 * kWarps;
 
 using namespace se::mma;
 
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // written by the kernel before this one: no __restrict__ (see the wait below)
                    const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                    const int* __restrict__ token_seq, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int page_size, float scale_log2, int window, int splits, int keys_per_split,
-                   int num_pages, int* __restrict__ error) {
-    constexpr int kChunks = D / 8;                   // 16-byte chunks per row
-    constexpr int kTileBytes = kTileKeys * D * 2;    // one K or V tile
+                   int num_pages, int* __restrict__ error, const SoftmaxOptions opt) {
+    constexpr int kTileBytes = kTileKeys * D * 2;    // one K tile
+    constexpr int kStageBytes = kTileKeys * (D + DV) * 2;    // a K tile and a V tile
     extern __shared__ __align__(128) uint8_t smem[];
 
     const int t = blockIdx.x;
@@ -54,24 +59,23 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
     const int ks = lo + split * keys_per_split;
     const int ke = min(pos + 1, ks + keys_per_split);
     const int* row_table = table + (size_t)seq_rows[token_seq[t]] * table_stride;
-    const size_t page_elems = (size_t)2 * hkv * page_size * D;
+    const size_t page_elems = (size_t)hkv * page_size * (D + DV);
     const size_t head_off = (size_t)kvh * page_size * D;
-    const size_t v_off = (size_t)hkv * page_size * D;
+    const size_t v_off = (size_t)hkv * page_size * D + (size_t)kvh * page_size * DV;
 
-    float o[D / 8][4];
+    float o[DV / 8][4];
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     const int num_tiles = ks < ke ? (ke - ks + kTileKeys - 1) / kTileKeys : 0;
 
-    auto load_tile = [&](int tile, int stage) {
-        uint8_t* kbase = smem + (size_t)stage * 2 * kTileBytes;
-        uint8_t* vbase = kbase + kTileBytes;
-        const int base = ks + tile * kTileKeys;
-        // A thread copies chunk (tid % kChunks) of rows tid / kChunks + k * (kThreads / kChunks).  The
-        // rows' addresses are looked up first (independent loads), so that no table load sits
-        // between the asynchronous copies.
+    // Rows [64][DIM] of a tile: a thread copies chunk (tid % chunks) of rows tid / chunks + k * (kThreads / chunks).
+    // The rows' addresses are looked up first (independent loads), so that no table load sits
+    // between the asynchronous copies.  `off`: where the head's rows start in a page; DIM elements a row.
+    auto load_rows = [&](auto dim_tag, uint8_t* dst, int base, size_t off) {
+        constexpr int DIM = decltype(dim_tag)::value;
+        constexpr int kChunks = DIM / 8;                 // 16-byte chunks per row
         constexpr int kRowStep = kThreads / kChunks, kIters = kTileKeys / kRowStep;
         static_assert(kThreads % kChunks == 0 && kTileKeys % kRowStep == 0, "tile copy mapping");
         const int c = threadIdx.x % kChunks, r0t = threadIdx.x / kChunks;
@@ -84,15 +88,19 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
             const int page = row_table[jj / page_size];
             // an entry that names no page of the pool is not followed: its rows are zero-filled
             page_ok[k] = page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_DECODE);
-            srcs[k] = cache + (size_t)(page_ok[k] ? page : 0) * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+            srcs[k] = cache + (size_t)(page_ok[k] ? page : 0) * page_elems + off + (size_t)(jj % page_size) * DIM + c * 8;
         }
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int r = r0t + k * kRowStep;
-            const bool ok = base + r < ke && page_ok[k];
-            cp_async16(smem_u32(kbase) + tile_off<D>(r, c), srcs[k], ok);
-            cp_async16(smem_u32(vbase) + tile_off<D>(r, c), srcs[k] + v_off, ok);
+            cp_async16(smem_u32(dst) + tile_off<DIM>(r, c), srcs[k], base + r < ke && page_ok[k]);
         }
+    };
+    auto load_tile = [&](int tile, int stage) {
+        uint8_t* kbase = smem + (size_t)stage * kStageBytes;
+        const int base = ks + tile * kTileKeys;
+        load_rows(std::integral_constant<int, D>{}, kbase, base, head_off);
+        load_rows(std::integral_constant<int, DV>{}, kbase + kTileBytes, base, v_off);
     };
 
     // Where the step's inputs are older than the kernel before this one (the one that writes the
@@ -130,7 +138,7 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
         cp_async_commit();
 
         const int stage = tile % kStages;
-        const uint32_t kaddr = smem_u32(smem + (size_t)stage * 2 * kTileBytes);
+        const uint32_t kaddr = smem_u32(smem + (size_t)stage * kStageBytes);
         const uint32_t vaddr = kaddr + kTileBytes;
         const int r0 = warp * 16;                       // this warp's 16 keys of the tile
         const int key0 = ks + tile * kTileKeys + r0;
@@ -143,6 +151,12 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
                 ldmatrix_x4(kaddr + tile_off<D>(r0 + (mat >> 1) * 8 + rr, 2 * kk + (mat & 1)), b0, b1, b2, b3);
                 mma_bf16(s[0], qa[kk], b0, b1);
                 mma_bf16(s[1], qa[kk], b2, b3);
+            }
+            if (opt.cap_in > 0.f) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] = capped_score(s[nt][e], opt.cap_in, opt.cap_out);
             }
             // mask keys beyond the range (rows share the token, hence the range)
             float mx[2] = {-INFINITY, -INFINITY};
@@ -179,15 +193,15 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
 #pragma unroll
             for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
 #pragma unroll
-            for (int i = 0; i < D / 8; ++i) {
+            for (int i = 0; i < DV / 8; ++i) {
                 o[i][0] *= corr[0]; o[i][1] *= corr[0];
                 o[i][2] *= corr[1]; o[i][3] *= corr[1];
             }
 #pragma unroll
-            for (int n2 = 0; n2 < D / 16; ++n2) {       // two 8-wide dim tiles per ldmatrix
+            for (int n2 = 0; n2 < DV / 16; ++n2) {      // two 8-wide dim tiles per ldmatrix
                 uint32_t b0, b1, b2, b3;
                 const int mat = lane >> 3, rr = lane & 7;
-                ldmatrix_x4_trans(vaddr + tile_off<D>(r0 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
+                ldmatrix_x4_trans(vaddr + tile_off<DV>(r0 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
                 mma_bf16(o[2 * n2], pa, b0, b1);
                 mma_bf16(o[2 * n2 + 1], pa, b2, b3);
             }
@@ -203,7 +217,7 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
     }
     float* sm_m = reinterpret_cast<float*>(smem);                 // [warps][16]
     float* sm_l = sm_m + kWarps * 16;
-    float* sm_o = sm_l + kWarps * 16;                             // [warps][16][D]
+    float* sm_o = sm_l + kWarps * 16;                             // [warps][16][DV]
     if (t4 == 0) {
         sm_m[warp * 16 + g] = m_run[0];
         sm_m[warp * 16 + g + 8] = m_run[1];
@@ -211,16 +225,16 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
         sm_l[warp * 16 + g + 8] = l_run[1];
     }
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
+    for (int i = 0; i < DV / 8; ++i) {
         const int c = i * 8 + 2 * t4;
-        float* r_lo = sm_o + ((size_t)warp * 16 + g) * D + c;
-        float* r_hi = sm_o + ((size_t)warp * 16 + g + 8) * D + c;
+        float* r_lo = sm_o + ((size_t)warp * 16 + g) * DV + c;
+        float* r_hi = sm_o + ((size_t)warp * 16 + g + 8) * DV + c;
         r_lo[0] = o[i][0]; r_lo[1] = o[i][1];
         r_hi[0] = o[i][2]; r_hi[1] = o[i][3];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < rows_valid * D; i += kThreads) {
-        const int r = i / D, d = i % D;
+    for (int i = threadIdx.x; i < rows_valid * DV; i += kThreads) {
+        const int r = i / DV, d = i % DV;
         float mt = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, sm_m[w * 16 + r]);
@@ -229,15 +243,19 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
         for (int w = 0; w < kWarps; ++w) {
             const float mw = sm_m[w * 16 + r];
             const float f = mw == -INFINITY ? 0.f : exp2f((mw - mt) * scale_log2);
-            acc += sm_o[((size_t)w * 16 + r) * D + d] * f;
+            acc += sm_o[((size_t)w * 16 + r) * DV + d] * f;
             lt += sm_l[w * 16 + r] * f;
         }
         const int head = head0 + r;
         if (splits == 1) {
-            out[((size_t)t * hq + head) * D + d] = __float2bfloat16_rn(acc / lt);
+            // the sink's term 2^(0 - mt): it grows beyond the type only where the keys hold nothing (the output is 0 then)
+            if (opt.sink) lt += exp2f(-mt * scale_log2);
+            float v = acc / lt;
+            if (opt.gate != nullptr) v = gated(v, opt.gate + (size_t)t * opt.gate_pitch + (size_t)head * DV + d);
+            out[((size_t)t * hq + head) * DV + d] = __float2bfloat16_rn(v);
         } else {
             const size_t pidx = ((size_t)t * hq + head) * splits + split;
-            part_o[pidx * D + d] = acc;
+            part_o[pidx * DV + d] = acc;
             if (d == 0) {
                 part_ml[pidx * 2] = mt == -INFINITY ? -INFINITY : mt * scale_log2;
                 part_ml[pidx * 2 + 1] = lt;
@@ -248,7 +266,7 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
 
 // out[t, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, int d, int splits) {
+                                    __nv_bfloat16* __restrict__ out, int d, int splits, int hq, const SoftmaxOptions opt) {
     grid_dependency_trigger();       // the output projection that follows may start streaming its weights
     const size_t th = blockIdx.x;
     float mt = -INFINITY;
@@ -262,35 +280,38 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
             acc += part_o[(th * splits + s) * d + i] * f;
             lt += part_ml[(th * splits + s) * 2 + 1] * f;
         }
-        out[th * d + i] = __float2bfloat16_rn(acc / lt);
+        if (opt.sink) lt += exp2f(-mt);
+        float v = acc / lt;
+        if (opt.gate != nullptr) v = gated(v, opt.gate + (th / hq) * opt.gate_pitch + (th % hq) * d + i);
+        out[th * d + i] = __float2bfloat16_rn(v);
     }
 }
 
-template <int D>
+template <int D, int DV>
 static int launch(const void* q, const void* cache, const int* table, int table_stride, const int* seq_rows,
                   const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int tokens,
                   int hq, int hkv, int page_size, float scale, int window, int splits, int keys_per_split,
-                  int num_pages, int* error, int settled, cudaStream_t stream) {
+                  int num_pages, int* error, int settled, const SoftmaxOptions& opt, cudaStream_t stream) {
     const int group = hq / hkv;
     const int gtiles = (group + 15) / 16;
-    const size_t stage_smem = (size_t)kStages * 2 * kTileKeys * D * 2;
-    const size_t merge_smem = (size_t)kWarps * 16 * (D + 2) * sizeof(float);
+    const size_t stage_smem = (size_t)kStages * kTileKeys * (D + DV) * 2;
+    const size_t merge_smem = (size_t)kWarps * 16 * (DV + 2) * sizeof(float);
     const size_t smem = stage_smem > merge_smem ? stage_smem : merge_smem;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(tokens, hkv * gtiles, splits);
     cudaError_t e = SE_LAUNCH_DEPENDENT_IF(
-        settled != 0, "attn", attn_decode_kernel<D>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q,
+        settled != 0, "attn", attn_decode_kernel<D, DV>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q,
         (const __nv_bfloat16*)cache, table, table_stride, seq_rows, token_seq, positions, (__nv_bfloat16*)out, part_o,
-        part_ml, hq, hkv, page_size, scale * 1.4426950408889634f, window, splits, keys_per_split, num_pages, error);
+        part_ml, hq, hkv, page_size, scale * 1.4426950408889634f, window, splits, keys_per_split, num_pages, error, opt);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1) {
-        attn_combine_kernel<<<tokens * hq, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, D, splits);
+        attn_combine_kernel<<<tokens * hq, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, DV, splits, hq, opt);
         e = cudaGetLastError();
     }
     return (int)e;
@@ -302,27 +323,39 @@ static int launch(const void* q, const void* cache, const int* table, int table_
 extern "C" int se_attn_decode_supported(int head_dim, int hq, int hkv) {
     return ((head_dim == 64 || head_dim == 128) && hkv > 0 && hq % hkv == 0) ? 1 : 0;
 }
+// the value head sizes the kernel takes beside a query/key head size it takes
+extern "C" int se_attn_decode_value_dim_supported(int v_head_dim) {
+    return (v_head_dim == 32 || v_head_dim == 64 || v_head_dim == 128) ? 1 : 0;
+}
 
-// part_o: float [tokens, hq, splits, head_dim]; part_ml: float [tokens, hq, splits, 2] (unused when splits == 1).
+// part_o: float [tokens, hq, splits, v_head_dim]; part_ml: float [tokens, hq, splits, 2] (unused when splits == 1).
 // keys_per_split is a multiple of 64; split s of a token covers keys lo + s*keys_per_split ...
 // settled: positions, token_seq, seq_rows and the block table were complete before the kernel
 // launched just before this one began (they are inputs of the step, and that kernel is the one
 // that writes the queries and the step's keys).  The attention kernel is then launched as that
 // kernel's dependent and reads them while it may still run; else it is launched the ordinary way.
+// softcap (0: none), sink, gate (nullptr: none) and gate_pitch: the softmax's options, as the plain kernel's.
 extern "C" int se_attn_decode(const void* q, const void* cache, const int* table, int table_stride,
                               const int* seq_rows, const int* token_seq, const int* positions, void* out,
-                              float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int page_size,
-                              float scale, int window, int splits, int keys_per_split, int num_pages, int* error,
-                              int settled, cudaStream_t stream) {
+                              float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int v_head_dim,
+                              int page_size, float scale, int window, int splits, int keys_per_split, int num_pages,
+                              int* error, int settled, float softcap, int sink, const void* gate, int gate_pitch,
+                              cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (!se_attn_decode_supported(head_dim, hq, hkv) || splits < 1 || keys_per_split <= 0 || keys_per_split % 64)
+    if (!se_attn_decode_supported(head_dim, hq, hkv) || !se_attn_decode_value_dim_supported(v_head_dim) || splits < 1 ||
+        keys_per_split <= 0 || keys_per_split % 64)
         return SE_ERR_UNSUPPORTED;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
-    if (head_dim == 64)
-        return se::dec::launch<64>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
-                                   tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, num_pages, error,
-                                   settled, stream);
-    return se::dec::launch<128>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o, part_ml,
-                                tokens, hq, hkv, page_size, scale, window, splits, keys_per_split, num_pages, error,
-                                settled, stream);
+    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * v_head_dim)) return SE_ERR_ARGUMENT;
+    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink,
+                                      (const __nv_bfloat16*)gate, gate_pitch};
+#define SE_DECODE_CASE(DQ, DVAL)                                                                                        \
+    if (head_dim == DQ && v_head_dim == DVAL)                                                                           \
+        return se::dec::launch<DQ, DVAL>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o,   \
+                                         part_ml, tokens, hq, hkv, page_size, scale, window, splits, keys_per_split,    \
+                                         num_pages, error, settled, opt, stream);
+    SE_DECODE_CASE(64, 64) SE_DECODE_CASE(128, 128) SE_DECODE_CASE(64, 32) SE_DECODE_CASE(64, 128)
+    SE_DECODE_CASE(128, 64) SE_DECODE_CASE(128, 32)
+#undef SE_DECODE_CASE
+    return SE_ERR_UNSUPPORTED;
 }

@@ -11,11 +11,14 @@
 // cache before this kernel runs.  Reference arithmetic:
 // src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127.
 //
-// Any page size; head sizes 64 and 128 (others use the plain kernel).  A block-table entry
-// outside [0, num_pages) is not followed: its rows are zero-filled and a code goes to the
-// error word.
+// Any page size; query/key head sizes 64 and 128, value head sizes 32, 64 and 128 (others use the
+// plain kernel): a page holds the keys [kv head][slot][D] and then the values [kv head][slot][DV].
+// The softmax's options (a cap on the scores, a sink of score 0, an output gate) are those of
+// mma_util.cuh's SoftmaxOptions.  A block-table entry outside [0, num_pages) is not followed: its
+// rows are zero-filled and a code goes to the error word.
 #include "common.cuh"
 #include "mma_util.cuh"
+#include <type_traits>
 
 namespace se {
 namespace pre {
@@ -28,15 +31,15 @@ constexpr int kThreads = 32 * kWarps;
 
 using namespace se::mma;
 
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(kThreads)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                     const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                     const int* __restrict__ cu_q, const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out,
                     int hq, int hkv, int page_size, float scale_log2, int window, int num_pages,
-                    int* __restrict__ error) {
-    constexpr int kChunks = D / 8;
-    constexpr int kTileBytes = kTileKeys * D * 2;
+                    int* __restrict__ error, const SoftmaxOptions opt) {
+    constexpr int kTileBytes = kTileKeys * D * 2;             // one K tile
+    constexpr int kStageBytes = kTileKeys * (D + DV) * 2;     // a K tile and a V tile
     extern __shared__ __align__(128) uint8_t smem[];
 
     // Blocks start in the order of their index, x fastest: the KV heads are x, and the row tiles
@@ -76,9 +79,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int num_tiles = (k_end - k_begin + kTileKeys - 1) / kTileKeys;
 
     const int* row_table = table + (size_t)seq_rows[entry] * table_stride;
-    const size_t page_elems = (size_t)2 * hkv * page_size * D;
+    const size_t page_elems = (size_t)hkv * page_size * (D + DV);
     const size_t head_off = (size_t)kvh * page_size * D;
-    const size_t v_off = (size_t)hkv * page_size * D;
+    const size_t v_off = (size_t)hkv * page_size * D + (size_t)kvh * page_size * DV;
 
     uint32_t qa[D / 16][4];
     {
@@ -93,21 +96,20 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
             qa[kk][3] = valid[1] ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
         }
     }
-    float o[D / 8][4];
+    float o[DV / 8][4];
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     int lo[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) lo[h] = window > 0 ? max(0, pos[h] - window + 1) : 0;
 
-    auto load_tile = [&](int tile, int stage) {
-        uint8_t* kbase = smem + (size_t)stage * 2 * kTileBytes;
-        uint8_t* vbase = kbase + kTileBytes;
-        const int base = k_begin + tile * kTileKeys;
-        // A thread copies chunk (tid % kChunks) of rows tid / kChunks + k * (kThreads / kChunks).  The
-        // rows' addresses are looked up first (independent loads), so that no table load sits
-        // between the asynchronous copies.
+    // Rows [64][DIM] of a tile: a thread copies chunk (tid % chunks) of rows tid / chunks + k * (kThreads / chunks).
+    // The rows' addresses are looked up first (independent loads), so that no table load sits
+    // between the asynchronous copies.  `off`: where the head's rows start in a page; DIM elements a row.
+    auto load_rows = [&](auto dim_tag, uint8_t* dst, int base, size_t off) {
+        constexpr int DIM = decltype(dim_tag)::value;
+        constexpr int kChunks = DIM / 8;
         constexpr int kRowStep = kThreads / kChunks, kIters = kTileKeys / kRowStep;
         static_assert(kThreads % kChunks == 0 && kTileKeys % kRowStep == 0, "tile copy mapping");
         const int c = threadIdx.x % kChunks, r0t = threadIdx.x / kChunks;
@@ -122,15 +124,20 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
             const int jj = min(max(j, k_lo), k_end - 1);
             const int page = row_table[jj / page_size];
             page_ok[k] = page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_PREFILL);
-            srcs[k] = cache + (size_t)(page_ok[k] ? page : 0) * page_elems + head_off + (size_t)(jj % page_size) * D + c * 8;
+            srcs[k] = cache + (size_t)(page_ok[k] ? page : 0) * page_elems + off + (size_t)(jj % page_size) * DIM + c * 8;
         }
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int r = r0t + k * kRowStep;
             const bool ok = base + r < k_end && base + r >= k_lo && page_ok[k];
-            cp_async16(smem_u32(kbase) + tile_off<D>(r, c), srcs[k], ok);
-            cp_async16(smem_u32(vbase) + tile_off<D>(r, c), srcs[k] + v_off, ok);
+            cp_async16(smem_u32(dst) + tile_off<DIM>(r, c), srcs[k], ok);
         }
+    };
+    auto load_tile = [&](int tile, int stage) {
+        uint8_t* kbase = smem + (size_t)stage * kStageBytes;
+        const int base = k_begin + tile * kTileKeys;
+        load_rows(std::integral_constant<int, D>{}, kbase, base, head_off);
+        load_rows(std::integral_constant<int, DV>{}, kbase + kTileBytes, base, v_off);
     };
 
     for (int s = 0; s < kStages - 1; ++s) {
@@ -150,7 +157,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         const int key0 = k_begin + tile * kTileKeys;
         if (key0 > warp_max_pos || row_base + warp * 16 >= total_rows) continue;   // warp-uniform: nothing visible
         const int stage = tile % kStages;
-        const uint32_t kaddr = smem_u32(smem + (size_t)stage * 2 * kTileBytes);
+        const uint32_t kaddr = smem_u32(smem + (size_t)stage * kStageBytes);
         const uint32_t vaddr = kaddr + kTileBytes;
 
         float s[kTileKeys / 8][4];
@@ -166,6 +173,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                 mma_bf16(s[2 * n2], qa[kk], b0, b1);
                 mma_bf16(s[2 * n2 + 1], qa[kk], b2, b3);
             }
+        }
+        if (opt.cap_in > 0.f) {
+#pragma unroll
+            for (int n = 0; n < kTileKeys / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] = capped_score(s[n][e], opt.cap_in, opt.cap_out);
         }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -203,17 +216,17 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
         for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
+        for (int i = 0; i < DV / 8; ++i) {
             o[i][0] *= corr[0]; o[i][1] *= corr[0];
             o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
 #pragma unroll
         for (int kk = 0; kk < kTileKeys / 16; ++kk) {
 #pragma unroll
-            for (int n2 = 0; n2 < D / 16; ++n2) {
+            for (int n2 = 0; n2 < DV / 16; ++n2) {
                 uint32_t b0, b1, b2, b3;
                 const int mat = lane >> 3, rr = lane & 7;
-                ldmatrix_x4_trans(vaddr + tile_off<D>(kk * 16 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
+                ldmatrix_x4_trans(vaddr + tile_off<DV>(kk * 16 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
                 mma_bf16(o[2 * n2], pa[kk], b0, b1);
                 mma_bf16(o[2 * n2 + 1], pa[kk], b2, b3);
             }
@@ -229,22 +242,32 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         if (!valid[h]) continue;
+        // the sink's term 2^(0 - m): it grows beyond the type only where the keys hold nothing (the output is 0 then)
+        if (opt.sink) l_run[h] += exp2f(-m_run[h] * scale_log2);
         const float inv = 1.f / l_run[h];
-        __nv_bfloat16* dst = out + ((size_t)tok[h] * hq + head[h]) * D;
+        __nv_bfloat16* dst = out + ((size_t)tok[h] * hq + head[h]) * DV;
+        const __nv_bfloat16* gp = opt.gate != nullptr ? opt.gate + (size_t)tok[h] * opt.gate_pitch + (size_t)head[h] * DV : nullptr;
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+        for (int i = 0; i < DV / 8; ++i) {
+            float a = o[i][2 * h] * inv, b = o[i][2 * h + 1] * inv;
+            if (gp != nullptr) {
+                a = gated(a, gp + i * 8 + 2 * t4);
+                b = gated(b, gp + i * 8 + 2 * t4 + 1);
+            }
+            *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = pack_bf16(a, b);
+        }
     }
 }
 
-template <int D>
+template <int D, int DV>
 static int launch(const void* q, const void* cache, const int* table, int table_stride, const int* seq_rows,
                   const int* cu_q, const int* kv_len, void* out, int entries, int max_q_len, int hq, int hkv,
-                  int page_size, float scale, int window, int num_pages, int* error, cudaStream_t stream) {
-    const size_t smem = (size_t)kStages * 2 * kTileKeys * D * 2;
+                  int page_size, float scale, int window, int num_pages, int* error, const SoftmaxOptions& opt,
+                  cudaStream_t stream) {
+    const size_t smem = (size_t)kStages * kTileKeys * (D + DV) * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -252,27 +275,35 @@ static int launch(const void* q, const void* cache, const int* table, int table_
     const int row_tiles = ceil_div(max_q_len * group, kTileRows);
     if (row_tiles > 65535) return SE_ERR_UNSUPPORTED;
     dim3 grid(hkv, row_tiles, entries);
-    attn_prefill_kernel<D><<<grid, kThreads, smem, stream>>>(
+    attn_prefill_kernel<D, DV><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
-        (__nv_bfloat16*)out, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages, error);
+        (__nv_bfloat16*)out, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages, error, opt);
     return (int)cudaGetLastError();
 }
 
 }  // namespace pre
 }  // namespace se
 
-// q, out: [tokens, hq, head_dim]; cu_q: [entries + 1] token offsets; kv_len: [entries] keys of each
-// request once this step's keys are written; seq_rows: [entries] block-table rows.
+// q: [tokens, hq, head_dim]; out: [tokens, hq, v_head_dim]; cu_q: [entries + 1] token offsets; kv_len: [entries]
+// keys of each request once this step's keys are written; seq_rows: [entries] block-table rows.
+// softcap (0: none), sink, gate (nullptr: none) and gate_pitch: the softmax's options, as the plain kernel's.
 extern "C" int se_attn_prefill(const void* q, const void* cache, const int* table, int table_stride,
                                const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int entries,
-                               int max_q_len, int hq, int hkv, int head_dim, int page_size, float scale, int window,
-                               int num_pages, int* error, cudaStream_t stream) {
+                               int max_q_len, int hq, int hkv, int head_dim, int v_head_dim, int page_size, float scale,
+                               int window, int num_pages, int* error, float softcap, int sink, const void* gate,
+                               int gate_pitch, cudaStream_t stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!(head_dim == 64 || head_dim == 128) || hkv <= 0 || hq % hkv || entries > 65535 || hkv > 65535)
         return SE_ERR_UNSUPPORTED;
-    if (head_dim == 64)
-        return se::pre::launch<64>(q, cache, table, table_stride, seq_rows, cu_q, kv_len, out, entries, max_q_len, hq,
-                                   hkv, page_size, scale, window, num_pages, error, stream);
-    return se::pre::launch<128>(q, cache, table, table_stride, seq_rows, cu_q, kv_len, out, entries, max_q_len, hq, hkv,
-                                page_size, scale, window, num_pages, error, stream);
+    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * v_head_dim)) return SE_ERR_ARGUMENT;
+    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink,
+                                      (const __nv_bfloat16*)gate, gate_pitch};
+#define SE_PREFILL_CASE(DQ, DVAL)                                                                                      \
+    if (head_dim == DQ && v_head_dim == DVAL)                                                                          \
+        return se::pre::launch<DQ, DVAL>(q, cache, table, table_stride, seq_rows, cu_q, kv_len, out, entries, max_q_len, \
+                                         hq, hkv, page_size, scale, window, num_pages, error, opt, stream);
+    SE_PREFILL_CASE(64, 64) SE_PREFILL_CASE(128, 128) SE_PREFILL_CASE(64, 32) SE_PREFILL_CASE(64, 128)
+    SE_PREFILL_CASE(128, 64) SE_PREFILL_CASE(128, 32)
+#undef SE_PREFILL_CASE
+    return SE_ERR_UNSUPPORTED;
 }

@@ -29,7 +29,10 @@
 // warp 11 those of tile 1 (S(j) first, then P·V of tile j-1 as its P arrives), independently
 // of one another; warps 2-5 and 6-9 are the softmax/epilogue warps of tiles 0 and 1.  A K/V
 // stage is free again when both issuers have committed its P·V.  Every mbarrier wait is
-// bounded and reports through the error word.  Arithmetic as the reference's prefill kernel
+// bounded and reports through the error word.  The softmax's options (a cap on the scores, a sink
+// of score 0, an output gate; mma_util.cuh's SoftmaxOptions) cost the softmax warps two more
+// special-function operations per score for the cap, one term in the last sum for the sink, and one
+// load and exponential per output element for the gate.  Arithmetic as the reference's prefill kernel
 // (src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127).
 #include "common.cuh"
 #include "mma_util.cuh"
@@ -143,7 +146,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                        const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out,
-                       int* error, int hq, int hkv, int page_size, float scale_log2, int window, int num_pages) {
+                       int* error, int hq, int hkv, int page_size, float scale_log2, int window, int num_pages,
+                       const se::mma::SoftmaxOptions opt) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;                               // [2 tiles][2 halves][128 rows][128 B]
@@ -331,6 +335,11 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(&bars.s_empty[x][b]));
+            if (opt.cap_in > 0.f) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c)
+                    sv[c] = __float_as_uint(se::mma::capped_score(__uint_as_float(sv[c]), opt.cap_in, opt.cap_out));
+            }
             const int key0 = k_begin + j * kKeys;
             // A tile every row of the warp sees in full needs no masking (rows ascend with the
             // lane: lane 0 has the smallest position, lane 31 the largest window start).
@@ -405,8 +414,12 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
         if (ok && mbar_wait(bar(&bars.o_done[x]), 0, &abort_s)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the sink's term 2^(0 - m): it grows beyond the type only where the keys hold nothing (the output is 0 then)
+            if (opt.sink) l += exp2f(-m_ref);
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D;
+            const __nv_bfloat16* gp = opt.gate != nullptr
+                ? opt.gate + (size_t)(tok0 + rr / group) * opt.gate_pitch + (size_t)(kvh * group + rr % group) * D : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t ov[32];
@@ -417,8 +430,14 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            w[i] = se::mma::pack_bf16(__uint_as_float(ov[c + 2 * i]) * inv, __uint_as_float(ov[c + 2 * i + 1]) * inv);
+                        for (int i = 0; i < 4; ++i) {
+                            float a = __uint_as_float(ov[c + 2 * i]) * inv, b = __uint_as_float(ov[c + 2 * i + 1]) * inv;
+                            if (gp != nullptr) {
+                                a = se::mma::gated(a, gp + c0 + c + 2 * i);
+                                b = se::mma::gated(b, gp + c0 + c + 2 * i + 1);
+                            }
+                            w[i] = se::mma::pack_bf16(a, b);
+                        }
                         *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
@@ -446,10 +465,14 @@ extern "C" int se_attn_prefill_tc_supported(int head_dim, int hq, int hkv) {
 extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* table, int table_stride,
                                   const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int* error,
                                   int entries, int max_q_len, int hq, int hkv, int head_dim, int page_size, float scale,
-                                  int window, int num_pages, cudaStream_t stream) {
+                                  int window, int num_pages, float softcap, int sink, const void* gate, int gate_pitch,
+                                  cudaStream_t stream) {
     using namespace se::fa;
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!se_attn_prefill_tc_supported(head_dim, hq, hkv) || entries > 65535 || hkv > 65535) return SE_ERR_UNSUPPORTED;
+    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * head_dim)) return SE_ERR_ARGUMENT;
+    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink,
+                                      (const __nv_bfloat16*)gate, gate_pitch};
     const size_t smem = (size_t)kTiles * kQBytes + kStages * kKVStageBytes + 1024;
     static bool configured = false;
     if (!configured) {
@@ -463,6 +486,6 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
     dim3 grid(hkv, row_tiles, entries);
     attn_prefill_tc_kernel<<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len,
-        (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages);
+        (__nv_bfloat16*)out, error, hq, hkv, page_size, scale * 1.4426950408889634f, window, num_pages, opt);
     return (int)cudaGetLastError();
 }

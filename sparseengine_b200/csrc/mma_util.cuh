@@ -34,10 +34,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Byte offset of 16-byte chunk `c` of row `r` in a [rows][D] bf16 tile whose chunks are
-// XOR-swizzled within each row (conflict-free ldmatrix).
+// XOR-swizzled within each row (conflict-free ldmatrix; rows of fewer than eight chunks swizzle
+// within what they have).
 template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
     constexpr int kChunks = D / 8;
-    return (uint32_t)((r * kChunks + (c ^ (r & 7))) * 16);
+    constexpr int kMask = kChunks < 8 ? kChunks - 1 : 7;
+    static_assert((kChunks & (kChunks - 1)) == 0, "rows of a power-of-two number of chunks");
+    return (uint32_t)((r * kChunks + (c ^ (r & kMask))) * 16);
+}
+
+// Options of the softmax that the tensor-core attention kernels share with the plain one.
+//   cap_in, cap_out : scale / c and c / scale for scores capped by c tanh(s * scale / c); 0, 0: no cap.
+//                     The kernels keep raw scores q.k and fold `scale` into their exponentials, so the
+//                     capped score goes back to raw units: s <- cap_out * tanh(s * cap_in).
+//   sink            : a key of score 0 without a value joins the softmax's denominator.
+//   gate, gate_pitch: the output is multiplied element by element with sigmoid(gate[t][h * dv + i])
+//                     (rows gate_pitch elements apart); nullptr: no gate.
+struct SoftmaxOptions {
+    float cap_in, cap_out;
+    int sink;
+    const __nv_bfloat16* gate;
+    int gate_pitch;
+};
+
+// cap_out * tanh(s * cap_in) with tanh(x) = 1 - 2 / (exp(2x) + 1); beyond |x| = 15 tanh is 1 in 32-bit.
+__device__ __forceinline__ float capped_score(float s, float cap_in, float cap_out) {
+    const float x = fminf(fmaxf(s * cap_in, -15.f), 15.f);
+    return cap_out * (1.f - __fdividef(2.f, __expf(2.f * x) + 1.f));
+}
+__device__ __forceinline__ float gated(float o, const __nv_bfloat16* gate) {
+    return o / (1.f + __expf(-__bfloat162float(*gate)));
 }
 
 }  // namespace mma

@@ -853,37 +853,57 @@ def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: i
     return splits, per_tiles * 64
 
 
+def _softmax_options(q, gate, num_heads, v_head_dim, softcap, sink):
+    """The tail of the tensor-core attention kernels' arguments: cap, sink, gate pointer, gate pitch."""
+    if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1 or gate.dtype != q.dtype
+                             or gate.shape[1] != num_heads * v_head_dim):
+        raise ValueError("gate must be a matrix [tokens, heads * value size] of q's dtype with contiguous rows")
+    return (float(softcap or 0.0), int(bool(sink)), gate.data_ptr() if gate is not None else None,
+            gate.stride(0) if gate is not None else 0)
+
+
+def attn_decode_value_dim_supported(v_head_dim: int) -> bool:
+    """Value head sizes the tensor-core kernels take beside a query/key head size they take."""
+    return v_head_dim in (32, 64, 128)
+
+
 def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads, head_dim, page_size,
-                scale, window=None, max_keys: int, num_pages=None, step_inputs_settled: bool = False):
+                scale, window=None, max_keys: int, num_pages=None, step_inputs_settled: bool = False, v_head_dim=None,
+                softcap=None, sink: bool = False, gate=None):
     """``step_inputs_settled``: ``table``, ``seq_rows``, ``token_seq`` and ``positions`` were complete
     before the kernel launched just before this call began (that kernel wrote ``q`` and the step's
     keys).  The attention kernel, launched as its dependent, then finds its place in the block table
-    while it still runs; otherwise it waits for it first."""
+    while it still runs; otherwise it waits for it first.  ``v_head_dim``, ``softcap``, ``sink`` and
+    ``gate`` as :func:`paged_attention_plain`'s."""
     tokens = q.shape[0]
+    dv = int(v_head_dim or head_dim)
     splits, per = attn_decode_plan(tokens, num_heads, num_kv_heads, max_keys, sms=sm_count(q.device))
     part_o = part_ml = None
     if splits > 1:
-        part_o = torch.empty(tokens * num_heads * splits * head_dim, dtype=torch.float32, device=q.device)
+        part_o = torch.empty(tokens * num_heads * splits * dv, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(tokens * num_heads * splits * 2, dtype=torch.float32, device=q.device)
-    _check(_fn("se_attn_decode", "pppipppppp" "iiiii" "f" "iii" "ip" "i" "p")(
+    _check(_fn("se_attn_decode", "pppipppppp" "iiiiii" "f" "iii" "ip" "i" "fipi" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml),
-        tokens, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), splits, per,
+        tokens, num_heads, num_kv_heads, head_dim, dv, page_size, float(scale), int(window or 0), splits, per,
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
-        int(bool(step_inputs_settled)), _stream()),
+        int(bool(step_inputs_settled)), *_softmax_options(q, gate, num_heads, dv, softcap, sink), _stream()),
         "attn_decode")
     return out
 
 
 def attn_prefill(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
-                 head_dim, page_size, scale, window=None, num_pages=None):
-    _check(_fn("se_attn_prefill", "pppipppp" "iiiiii" "f" "i" "ip" "p")(
+                 head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
+                 sink: bool = False, gate=None):
+    dv = int(v_head_dim or head_dim)
+    _check(_fn("se_attn_prefill", "pppipppp" "iiiiiii" "f" "i" "ip" "fipi" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), entries, max_q_len, num_heads,
-        num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)), _stream()), "attn_prefill")
+        num_kv_heads, head_dim, dv, page_size, float(scale), int(window or 0),
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
+        *_softmax_options(q, gate, num_heads, dv, softcap, sink), _stream()), "attn_prefill")
     return out
 
 
@@ -893,14 +913,18 @@ def attn_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int) 
 
 
 def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
-                    head_dim, page_size, scale, window=None, num_pages=None):
-    """Prompt-portion attention on tcgen05 (head size 128)."""
-    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ii" "p")(
+                    head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
+                    sink: bool = False, gate=None):
+    """Prompt-portion attention on tcgen05 (head size 128, values of the same size)."""
+    if int(v_head_dim or head_dim) != head_dim:
+        raise ValueError("the tcgen05 prompt kernel takes values of the keys' head size")
+    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ii" "fipi" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(q.device)),
         entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-        cache.shape[0] if num_pages is None else int(num_pages), _stream()),
+        cache.shape[0] if num_pages is None else int(num_pages),
+        *_softmax_options(q, gate, num_heads, head_dim, softcap, sink), _stream()),
         "attn_prefill_tc")
     return out
 

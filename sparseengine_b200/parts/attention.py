@@ -178,23 +178,23 @@ class PagedAttention(Mixer):
         ``q``; the split-key kernel then looks its place in the block table up while it still runs.
         ``gate``: the output gate's projection (a view with a row pitch), or None."""
         s = self.spec
-        variant = s.score_softcap is not None or s.sink is not None or gate is not None
-        if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16 and s.value_dim == s.head_dim
-                and not variant
-                and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)):
+        options = dict(v_head_dim=s.value_dim, softcap=s.score_softcap, sink=s.sink == "zero", gate=gate)
+        if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16
+                and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)
+                and ops.attn_decode_value_dim_supported(s.value_dim)):
             if not self.takes_portion_kernel(step):
                 max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
                 ops.attn_decode(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                 num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
                                 page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys,
-                                step_inputs_settled=after_qk_prep)
+                                step_inputs_settled=after_qk_prep, **options)
             else:
-                # prompt portions: tcgen05 + tensor memory for head size 128, m16n8k16 tiles otherwise
-                fn = (ops.attn_prefill_tc if ops.attn_prefill_tc_supported(s.head_dim, s.num_heads, s.num_kv_heads)
-                      else ops.attn_prefill)
+                # prompt portions: tcgen05 + tensor memory for head size 128 (values as wide), m16n8k16 tiles otherwise
+                fn = (ops.attn_prefill_tc if s.value_dim == s.head_dim
+                      and ops.attn_prefill_tc_supported(s.head_dim, s.num_heads, s.num_kv_heads) else ops.attn_prefill)
                 fn(q, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, out, entries=step.num_seqs,
                    max_q_len=step.max_q_len, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
-                   head_dim=s.head_dim, page_size=slot.page_size, scale=s.scale, window=s.window)
+                   head_dim=s.head_dim, page_size=slot.page_size, scale=s.scale, window=s.window, **options)
             return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,

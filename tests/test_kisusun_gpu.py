@@ -1,0 +1,579 @@
+"""The Kisusun design in the engine against the plain implementation (tests/plain_kisusun.py):
+each mechanism alone, whole prompts against token-by-token decoding, portions down to two tokens,
+mixed batches with pages and rows that are used again, far keys and page borders, both sides of
+the window's edge, the sink, the cap, blended values, grouped routing, the first tokens of a
+sequence, long decoding, other sizes (also values equal to one another or to 1), and greedy
+generation through ``LLM``."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kisusun as pk
+import trace_util as tu
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def attn(heads, kv, dim, vdim, window=None, rot=None, factor=None, base=10000.0, scale=None, cap=None, mix=False, mlp=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale if scale is not None else dim ** -0.5,
+         "v_mix": mix}
+    if window is not None:
+        m["mask"] = {"size": window}
+    if rot:
+        m["rot"] = {"base": base, "dims": rot}
+        if factor is not None:
+            m["rot"]["scaling"] = {"factor": factor}
+    if cap is not None:
+        m["softcap"] = cap
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(experts, top, ff, limit=1.5, groups=None, keep=None, scale=1.0, shared=None, shared_limit=3.0):
+    router = {"experts": experts, "top": top, "scale": scale}
+    if groups is not None:
+        router["groups"] = {"count": groups, "keep": keep}
+    out = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": router}
+    if shared:
+        out["shared"] = {"ff": shared, "limit": shared_limit}
+    return out
+
+
+def config(width, vocab, layers, embed_scale=4.0, logit_scale=0.5, eps=1e-5):
+    return {"architecture": "Kisusun", "vocab": vocab, "width": width, "layers": layers, "logit_scale": logit_scale,
+            "embedding": {"scale": embed_scale}, "norm": {"eps": eps}}
+
+
+CONFIGS = {
+    # everything at once: partial rotation with a factor, cap, window, blended values from the second layer on,
+    # a dense layer, grouped routing with a shared expert, a layer without feed-forward
+    "all": config(96, 160, [
+        attn(6, 3, 32, 16, window=23, rot=16, factor=2.0, cap=10.0, mlp=dense(128)),
+        attn(6, 3, 32, 16, window=23, rot=16, factor=2.0, cap=10.0, mix=True, mlp=moe(8, 3, 48, groups=4, keep=2, scale=1.5, shared=64)),
+        attn(6, 3, 32, 16, window=40, rot=32, base=500.0, cap=6.0, mix=True),
+        attn(6, 3, 32, 16, window=23, rot=16, factor=2.0, cap=10.0, mix=True, mlp=moe(8, 3, 48, groups=2, keep=1, scale=1.5, shared=64)),
+    ]),
+    # head sizes the tensor-core attention kernels take in bfloat16 (64 and 128), values as wide as keys
+    "wide": config(128, 200, [
+        attn(4, 1, 64, 64, window=50, rot=32, factor=4.0, cap=20.0, mix=True, mlp=moe(6, 2, 64, groups=3, keep=2, shared=128)),
+        attn(2, 1, 128, 128, window=33, rot=128, cap=15.0, mlp=dense(192)),
+        attn(4, 1, 64, 64, window=50, rot=64, cap=20.0, mix=True, mlp=dense(96)),
+    ], embed_scale=8.0),
+    # sizes that are equal or 1: one head, one expert of which one is chosen, one group, a window of 1, factor 1
+    "ones": config(64, 96, [
+        attn(1, 1, 16, 16, window=1, rot=16, factor=1.0, cap=1.0, scale=1.0, mix=True, mlp=moe(1, 1, 64, limit=1.0)),
+        attn(1, 1, 16, 16, window=2, rot=2, cap=30.0, mix=True, mlp=moe(4, 4, 16, groups=1, keep=1, shared=16, shared_limit=1.0)),
+        attn(2, 2, 8, 8, window=64, mix=False, mlp=moe(4, 1, 16, groups=4, keep=1)),
+    ], embed_scale=1.0, logit_scale=1.0),
+    # sizes that are multiples of nothing in particular
+    "odd": config(52, 77, [
+        attn(3, 1, 20, 12, window=11, rot=6, factor=3.0, cap=7.0, mlp=moe(6, 2, 30, groups=3, keep=2, scale=0.7, shared=22)),
+        attn(3, 1, 20, 12, window=29, rot=10, cap=5.0, mix=True, mlp=dense(50)),
+        attn(5, 5, 10, 6, window=17, rot=10, base=77.0, cap=9.0, mlp=moe(9, 3, 18, groups=3, keep=1, scale=2.5)),
+        attn(3, 1, 20, 12, window=11, rot=20, cap=7.0, mix=True),
+    ], embed_scale=2.0, logit_scale=2.0, eps=1e-3),
+}
+
+
+def write_folder(folder, cfg, seed, w=None):
+    from safetensors.torch import save_file
+    w = w if w is not None else pk.random_weights(cfg, seed)
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.contiguous() for k, v in w.items()}, os.path.join(folder, "model.safetensors"))
+    return w
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for i, (name, cfg) in enumerate(CONFIGS.items()):
+        d = str(tmp_path_factory.mktemp("kis_" + name))
+        out[name] = (d, cfg, write_folder(d, cfg, 31 + i))
+    return out
+
+
+_plain_cache = {}
+
+
+def plain_logits(name, cfg, w, seqs, margins=None):
+    """{id: logits [T, vocab]}; ``margins`` (a dict) receives {id: [T]}, the smallest distance by which a
+    router of the plain implementation made a choice for that token."""
+    out = {}
+    for sid, toks in seqs.items():
+        key = (json.dumps(cfg, sort_keys=True), sum(float(v.float().sum()) for v in w.values()), tuple(toks))
+        if key not in _plain_cache:
+            ms = []
+            logits = pk.forward(cfg, w, toks, margins=ms).float().numpy()
+            own = torch.stack(ms).min(0).values if ms else torch.full((len(toks),), float("inf"), dtype=torch.float64)
+            _plain_cache[key] = (logits, own.numpy())
+        out[sid] = _plain_cache[key][0]
+        if margins is not None:
+            margins[sid] = _plain_cache[key][1]
+    return out
+
+
+def row_errors(got, ref):
+    """Worst difference of a logits row (mean taken off, root mean square) in units of the
+    reference rows' root mean square; also where it is."""
+    rows = np.stack([ref[sid][p] for sid, p in got])
+    rms = float(np.sqrt((rows.astype(np.float64) ** 2).mean()))
+    worst, where = 0.0, None
+    for (sid, p), row in got.items():
+        d = row.astype(np.float64) - ref[sid][p]
+        d -= d.mean()
+        e = float(np.sqrt((d * d).mean())) / rms
+        if not e == e:
+            e = float("inf")
+        if e > worst:
+            worst, where = e, (sid, p)
+    return worst, where
+
+
+# bfloat16: what rounding alone does to these small models; the 32-bit runs carry the sharp bound
+BOUND = {"float32": 3e-5, "bfloat16": 6e-2}
+# A router's choice that hangs on less than this (in scores) can turn under the rounding of the type.
+# The plain implementation knows where such choices are.  In 32-bit they are rare, and a row is left out
+# if it or any token before it has one (it may attend to that token).  In bfloat16 about one token in ten
+# has one: the token's own row is then held to LOOSE only, and the rows after it to the type's bound (a
+# turned choice changes one expert's share of one token's update, which later tokens see through one of
+# many attention weights: far inside that bound).
+CLOSE_CALL = {"float32": 2e-5, "bfloat16": 4e-3}
+LOOSE = 0.5
+MIN_CLEAR = {"float32": 0.9, "bfloat16": 0.5}
+
+
+def make_runner(folder, dtype, steps, page_size=16, rows=4, **kw):
+    from sparseengine_b200.engine.factory import build_runner
+    tokens = tu.max_live_tokens(steps, round_to=page_size)
+    return build_runner(folder, dtype=dtype, page_size=page_size, num_pages=max(1, tokens // page_size), max_rows=rows,
+                        max_seq_len=max(64, tokens), **kw)
+
+
+def check_trace(folders, name, dtype, steps, seqs, what, bound=None, **kw):
+    folder, cfg, w = folders[name]
+    runner = make_runner(folder, dtype, steps, **kw)
+    got = tu.run_trace_runner(runner, steps)
+    from sparseengine_b200.csrc import ops
+    ops.error_check(runner.device)
+    runner.cache.check()
+    assert runner.cache.free_rows == runner.cache.max_rows
+    margins = {}
+    ref = plain_logits(name, cfg, w, seqs, margins)
+    if dtype == "float32":
+        margins = {sid: np.minimum.accumulate(m) for sid, m in margins.items()}
+    clear = {k: v for k, v in got.items() if margins[k[0]][k[1]] > CLOSE_CALL[dtype]}
+    assert len(clear) >= MIN_CLEAR[dtype] * len(got), (len(clear), len(got))
+    worst, where = row_errors(clear, ref)
+    assert worst < (bound or BOUND[dtype]), f"{what} ({name}, {dtype}): row error {worst:.3e} at {where}"
+    worst, where = row_errors(got, ref)
+    assert worst < max(LOOSE, bound or 0.0), f"{what} ({name}, {dtype}): row error {worst:.3e} at {where} (close calls included)"
+    return runner
+
+
+def prompts(cfg, lengths, seed):
+    return {f"s{i}": tu.random_prompt(cfg["vocab"], n, seed + i) for i, n in enumerate(lengths)}
+
+
+CUTS = (tu.trace_whole, lambda s: tu.trace_chunks(s, sizes=(2, 3, 1, 5, 2)), lambda s: tu.trace_tail_decode(s, tail=9))
+
+
+# ---- each mechanism alone ----------------------------------------------------------------------
+
+SINGLE = {
+    "attention_bare": [attn(4, 2, 16, 24)],
+    "rotation_partial_scaled": [attn(2, 2, 16, 16, rot=8, factor=4.0, base=100.0)],
+    "rotation_whole_head": [attn(2, 1, 16, 8, rot=16)],
+    "cap": [attn(2, 1, 16, 16, scale=2.0, cap=1.5)],
+    "window": [attn(2, 2, 16, 16, window=5)],
+    "blended_values": [attn(2, 1, 16, 8), attn(2, 1, 16, 8, mix=True), attn(2, 1, 16, 8, mix=True), attn(2, 1, 16, 8, mix=True)],
+    "dense_feed_forward": [attn(1, 1, 8, 8, mlp=dense(80))],
+    "routed_feed_forward": [attn(1, 1, 8, 8, mlp=moe(6, 3, 16, scale=2.0))],
+    "grouped_routing": [attn(1, 1, 8, 8, mlp=moe(12, 4, 16, groups=4, keep=2))],
+    "shared_expert": [attn(1, 1, 8, 8, mlp=moe(4, 1, 16, limit=0.5, shared=24, shared_limit=0.7))],
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", sorted(SINGLE))
+def test_each_mechanism_alone(tmp_path, which, dtype):
+    cfg = config(40, 50, SINGLE[which], embed_scale=3.0)
+    w = write_folder(str(tmp_path), cfg, 5)
+    seqs = prompts(cfg, (37, 1, 18), 3)
+    for cut in CUTS:
+        check_trace({which: (str(tmp_path), cfg, w)}, which, dtype, cut(seqs), seqs, "alone")
+
+
+def test_the_plain_mechanisms_matter():
+    """The premise of the tests above: on the plain implementation, taking a mechanism out moves the
+    logits far beyond the bounds used here."""
+    def moved(layers, change):
+        cfg = config(40, 50, layers, embed_scale=3.0)
+        w = pk.random_weights(cfg, 5)
+        toks = tu.random_prompt(50, 37, 3)
+        a = pk.forward(cfg, w, toks)
+        other = json.loads(json.dumps(cfg))
+        change(other, w)
+        b = pk.forward(other, w, toks)
+        return float((a - b).abs().max() / a.abs().max())
+
+    assert moved(SINGLE["cap"], lambda c, w: c["layers"][0]["mixer"].pop("softcap")) > 1e-2
+    assert moved(SINGLE["window"], lambda c, w: c["layers"][0]["mixer"]["mask"].update(size=6)) > 1e-2
+    assert moved(SINGLE["rotation_partial_scaled"], lambda c, w: c["layers"][0]["mixer"]["rot"].pop("scaling")) > 1e-3
+    assert moved(SINGLE["blended_values"], lambda c, w: c["layers"][3]["mixer"].update(v_mix=False)) > 1e-2
+    assert moved(SINGLE["grouped_routing"], lambda c, w: c["layers"][0]["mlp"]["router"].pop("groups")) > 1e-2
+    assert moved(SINGLE["shared_expert"], lambda c, w: c["layers"][0]["mlp"].pop("shared")) > 1e-2
+
+
+def test_norm_into_the_stream_alone():
+    from sparseengine_b200.csrc import ops
+    g = torch.Generator().manual_seed(1)
+    for rows, width, eps in ((5, 40, 1e-5), (3, 7, 1e-2), (2, 1024, 1e-6)):
+        stream = torch.randn(rows, width, generator=g)
+        y = torch.randn(rows, width, generator=g).to(torch.bfloat16)
+        w = (1 + 0.3 * torch.randn(width, generator=g)).to(torch.bfloat16)
+        want = stream.double() + pk.rms_norm(y.double(), w.double(), eps)
+        s = stream.to(DEV).clone()
+        act = torch.empty(rows, width, dtype=torch.bfloat16, device=DEV)
+        ops.rmsnorm_add_stream(s, y.to(DEV), w.to(DEV), eps, out_act=act)
+        assert float((s.cpu().double() - want).abs().max()) < 1e-5
+        assert torch.equal(act.cpu(), want.float().to(torch.bfloat16)) or float((act.cpu().double() - want).abs().max()) < 4e-2
+        s32 = stream.to(DEV).clone()
+        ops.rmsnorm_add_stream(s32, y.float().to(DEV), w.float().to(DEV), eps)
+        assert float((s32.cpu().double() - want).abs().max()) < 1e-5
+
+
+def test_grouped_selection_alone():
+    """The router's selection from given logits against the plain one, where groups decide: the
+    best expert of all sits in a group whose two best sum to less than another group's."""
+    from sparseengine_b200.csrc import ops
+    scores = torch.tensor([[0.9, 0.1, 0.12, 0.14, 0.6, 0.62, 0.5, 0.16],          # group 1 wins: 1.22 against 1.04
+                           [0.9, 0.4, 0.12, 0.1, 0.6, 0.62, 0.5, 0.14],           # group 0 wins: 1.3 against 1.22
+                           [0.2, 0.3, 0.25, 0.1, 0.02, 0.5, 0.01, 0.015]])        # group 1: 0.52 against 0.55 -> group 0
+    logits = torch.log(scores / (1 - scores))
+    w = {"router": torch.eye(8, dtype=torch.float64)}
+    for count, keep, top in ((2, 1, 3), (4, 2, 2), (8, 3, 3), (1, 1, 3), (4, 4, 5)):
+        router = {"experts": 8, "top": top, "scale": 2.5, "groups": {"count": count, "keep": keep}}
+        want_ids, want_w = pk.route(logits.double(), w, "", router)
+        ids = torch.empty(3, top, dtype=torch.int32, device=DEV)
+        wt = torch.empty(3, top, dtype=torch.float32, device=DEV)
+        ops.router_select(logits.float().to(DEV), None, ids, wt, top_k=top, score_fn="sigmoid", renormalize=False,
+                          routed_scale=2.5, groups=count, keep_groups=keep)
+        assert torch.equal(ids.cpu().long().sort(-1).values, want_ids.sort(-1).values), (count, keep, top)
+        got = torch.zeros(3, 8).scatter_(1, ids.cpu().long(), wt.cpu())
+        ref = torch.zeros(3, 8, dtype=torch.float64).scatter_(1, want_ids, want_w)
+        assert float((got.double() - ref).abs().max()) < 1e-5
+    # the first row's best expert is left out when its group loses
+    router = {"experts": 8, "top": 3, "groups": {"count": 2, "keep": 1}}
+    assert 0 not in pk.route(logits.double(), w, "", router)[0][0].tolist()
+
+
+def test_clamped_expert_alone():
+    """The experts' gated activation with its clamps against the plain form, through the feed-forward
+    part of the engine (one expert that every token uses), at pre-activations far outside the limit."""
+    from sparseengine_b200.config.specs import DenseMLPSpec
+    from sparseengine_b200.parts.moe import DenseMLP
+    g = torch.Generator().manual_seed(2)
+    width, ff, limit = 24, 40, 0.8
+    w = {"gate": torch.randn(ff, width, generator=g).to(torch.bfloat16), "up": torch.randn(ff, width, generator=g).to(torch.bfloat16),
+         "down": (torch.randn(width, ff, generator=g) / 6).to(torch.bfloat16)}
+    h = torch.randn(9, width, generator=g).to(torch.bfloat16)
+    want = pk.clamped_expert(h.double(), {k: v.double() for k, v in w.items()}, "", limit)
+    pre = h.double() @ w["gate"].double().T
+    assert float((pre > limit).double().mean()) > 0.2 and float((pre < -limit).double().mean()) > 0.2
+    for dtype in (torch.float32, torch.bfloat16):
+        part = DenseMLP(DenseMLPSpec(hidden_size=width, intermediate_size=ff, activation="clamped_swiglu", activation_limit=limit,
+                                     activation_alpha=pk.EXPERT_SLOPE), dtype)
+        part.bind({"w13": torch.cat([w["gate"], w["up"]], 0)[None].to(DEV, dtype).contiguous(),
+                   "w2": w["down"][None].to(DEV, dtype).contiguous()})
+        got = part.forward(h.to(DEV, dtype), None)
+        tol = 2e-5 if dtype == torch.float32 else 3e-2
+        assert float((got.cpu().double() - want).abs().max()) < tol * float(want.abs().max()), dtype
+
+
+# ---- ways of cutting ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_decode_chunks_mixed(folders, name, dtype):
+    cfg = CONFIGS[name]
+    seqs = prompts(cfg, (70, 33, 1, 18, 49, 2, 26), 20)
+    check_trace(folders, name, dtype, tu.trace_whole(seqs), seqs, "whole")
+    check_trace(folders, name, dtype, tu.trace_tail_decode(seqs, tail=20), seqs, "decode")
+    check_trace(folders, name, dtype, tu.trace_chunks(seqs), seqs, "portions")
+    check_trace(folders, name, dtype, tu.trace_chunks(seqs, sizes=(2,)), seqs, "portions of two")
+    # three rows for seven requests, and a pool of the live tokens only: rows and pages are used again
+    runner = check_trace(folders, name, dtype, tu.trace_mixed(seqs, live=3, chunk=6, decode_tail=5), seqs, "mixed", rows=3)
+    assert all(g.pool.reused_total > 0 for g in runner.cache.groups)
+    check_trace(folders, name, dtype, tu.trace_random(seqs, seed=3, live=4), seqs, "random schedule", page_size=8)
+
+
+def test_one_row_and_its_pages_used_again(folders):
+    """One row: every request gets the row and the pages the one before it left, a long request first."""
+    seqs = prompts(CONFIGS["all"], (60, 5, 1, 9), 44)
+    check_trace(folders, "all", "float32", tu.trace_chunks(seqs, sizes=(7, 2)), seqs, "one row", rows=1)
+
+
+# ---- places where a fault would sit --------------------------------------------------------------
+
+def sharp_model(window, heads=4, kv=2, dim=32, vdim=32, cap=None, seed=9):
+    """One attention layer whose softmax is sharp (a large score scale), so that a query hangs on the
+    one or two keys of its window with the highest score: a key that is lost at the window's far edge,
+    one that is let in from beyond it, or one read from the wrong place of a page moves the row by
+    much.  Then a blending layer, so that a value cached at the wrong place shows as well."""
+    cfg = config(64, 80, [attn(heads, kv, dim, vdim, window=window, scale=1.5, cap=cap, mix=True, mlp=dense(64)),
+                          attn(heads, kv, dim, vdim, window=window, scale=1.5, cap=cap, mix=True)], embed_scale=6.0)
+    return cfg, pk.random_weights(cfg, seed)
+
+
+def test_sharp_attention_hangs_on_few_keys_over_the_whole_window():
+    """The premise of the tests below, on the plain implementation: the heaviest key of a late query
+    carries a large share of the weight, lies anywhere in the window (often more than 64 back), and the
+    keys at the window's two edges are the heaviest often enough."""
+    window = 150
+    cfg, w = sharp_model(window)
+    wd = {k: v.double() for k, v in w.items()}
+    T = 415
+    toks = torch.tensor(tu.random_prompt(80, T, 60))
+    x = wd["embed"][toks] * cfg["embedding"]["scale"]
+    m = cfg["layers"][0]["mixer"]
+    q = pk.rms_norm(x @ wd["l0.mix.q"].T, wd["l0.mix.q.norm"], 1e-5).view(T, 4, 32)
+    k = pk.rms_norm(x @ wd["l0.mix.k"].T, wd["l0.mix.k.norm"], 1e-5).view(T, 2, 32)
+    s = (q[:, 0] @ k[:, 0].T) * m["scale"]
+    p = pk.softmax_plus_one(s, pk.seen_keys(T, window))
+    late = torch.arange(T) >= 200
+    assert float(p.max(-1).values[late].mean()) > 0.15
+    back = (torch.arange(T) - p.argmax(-1))[late]
+    assert float((back > 64).float().mean()) > 0.4 and int(back.max()) == window - 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,sizes", [(37, (4, 2, 32, 32)), (150, (4, 2, 32, 32)), (64, (4, 1, 64, 64)), (70, (2, 1, 128, 128)),
+                                          (129, (4, 2, 64, 32))])
+def test_the_windows_edge_far_keys_and_page_borders(tmp_path, dtype, window, sizes):
+    """The oldest key a query sees wanders through every place of a page, in prompts, in portions that
+    start and end anywhere, and in tokens decoded alone; prompts end around page borders and around the
+    window's length.  Head sizes 64 and 128 take the tensor-core kernels in bfloat16.  (In bfloat16 the
+    rounding of queries and keys moves such sharp weights by itself, hence the wider bound there; a lost
+    key moves the row by its whole size.)"""
+    cfg, w = sharp_model(window, *sizes)
+    write_folder(str(tmp_path), cfg, 0, w)
+    seqs = prompts(cfg, (window + 190, window, window + 1, window - 1, 16, 17, 95), 60)
+    fs = {"edge": (str(tmp_path), cfg, w)}
+    bound = 0.3 if dtype == "bfloat16" else None
+    check_trace(fs, "edge", dtype, tu.trace_whole(seqs), seqs, "window, whole", bound)
+    check_trace(fs, "edge", dtype, tu.trace_tail_decode(seqs, tail=window + 30), seqs, "window, decoded", bound)
+    check_trace(fs, "edge", dtype, tu.trace_chunks(seqs, sizes=(15, 2, 16, 33, 1, window, window + 1, 64)), seqs,
+                "window, portions", bound)
+    check_trace(fs, "edge", dtype, tu.trace_mixed(seqs, live=3, chunk=21, decode_tail=window + 3), seqs, "window, mixed", bound, rows=3)
+    # the plain implementation itself is sensitive to one key more or less
+    other = json.loads(json.dumps(cfg))
+    for layer in other["layers"]:
+        layer["mixer"]["mask"]["size"] = window + 1
+    a, b = pk.forward(cfg, w, seqs["s0"]), pk.forward(other, w, seqs["s0"])
+    assert float((a - b)[window:].abs().max() / a.abs().max()) > 0.05
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 16), (4, 1, 64, 64)])
+def test_the_sink_takes_its_share(tmp_path, dtype, sizes):
+    """Queries scaled so that every score is far below zero in one head and far above in another: in
+    the first the sink takes all of the weight (the head's output vanishes), in the second none; windows
+    of one key and of two.  A softmax without the sink gives weights that sum to one in both."""
+    heads, kv, dim, vdim = sizes
+    cfg = config(48, 64, [attn(heads, kv, dim, vdim, window=2, mlp=dense(32)), attn(heads, kv, dim, vdim, window=1, mix=False)])
+    w = pk.random_weights(cfg, 4)
+    for i in range(2):
+        # keys normed to all-positive rows, queries all-positive or all-negative per head
+        w[f"l{i}.mix.k.norm"] = torch.ones(kv * dim, dtype=torch.bfloat16)
+        w[f"l{i}.mix.k"] = w[f"l{i}.mix.k"].abs()
+        w[f"l{i}.mix.q"] = w[f"l{i}.mix.q"].abs()
+        sign = torch.ones(heads, dim)
+        sign[0] = -1.0
+        w[f"l{i}.mix.q.norm"] = (sign.reshape(-1) * 3.0).to(torch.bfloat16)
+    w["embed"] = w["embed"].abs()
+    write_folder(str(tmp_path), cfg, 0, w)
+    seqs = prompts(cfg, (21, 2, 1), 7)
+    fs = {"sink": (str(tmp_path), cfg, w)}
+    for cut in CUTS:
+        check_trace(fs, "sink", dtype, cut(seqs), seqs, "sink")
+    # premise: in head 0 the seen keys together hold almost nothing
+    wd = {k: v.double() for k, v in w.items()}
+    x = wd["embed"][torch.tensor(seqs["s0"])] * cfg["embedding"]["scale"]
+    q = pk.rms_norm(x @ wd["l0.mix.q"].T, wd["l0.mix.q.norm"], 1e-5).view(21, heads, dim)
+    k = pk.rms_norm(x @ wd["l0.mix.k"].T, wd["l0.mix.k.norm"], 1e-5).view(21, kv, dim)
+    s0 = (q[:, 0] @ k[:, 0].T) * cfg["layers"][0]["mixer"]["scale"]
+    assert float(pk.softmax_plus_one(s0, pk.seen_keys(21, 2)).sum(-1).max()) < 0.05
+    s1 = (q[:, 1] @ k[:, 0].T) * cfg["layers"][0]["mixer"]["scale"]
+    assert float(pk.softmax_plus_one(s1, pk.seen_keys(21, 2)).sum(-1).min()) > 0.95
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 16), (2, 1, 64, 64)])
+def test_scores_far_beyond_the_cap(tmp_path, dtype, sizes):
+    """A score scale that puts most raw scores far beyond the cap: the weights are those of scores
+    squeezed into (-cap, cap), far from the raw ones'."""
+    heads, kv, dim, vdim = sizes
+    cfg = config(48, 64, [attn(heads, kv, dim, vdim, window=40, scale=3.0, cap=2.0, rot=8, mlp=dense(32))])
+    w = write_folder(str(tmp_path), cfg, 6)
+    seqs = prompts(cfg, (90, 7), 11)
+    fs = {"cap": (str(tmp_path), cfg, w)}
+    for cut in (tu.trace_whole, lambda s: tu.trace_chunks(s, sizes=(2, 9, 31)), lambda s: tu.trace_tail_decode(s, tail=45)):
+        check_trace(fs, "cap", dtype, cut(seqs), seqs, "cap")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_blending_takes_the_first_blending_layers_values(tmp_path, dtype):
+    """Blending weights near one: a layer's cached values are almost the first blending layer's, so
+    values taken from the layer before, from layer 0 (which does not blend), or from another token show."""
+    layers = [attn(2, 1, 16, 8, window=9)] + [attn(2, 1, 16, 8, window=9, mix=True, mlp=dense(32) if i == 1 else None) for i in range(4)]
+    cfg = config(40, 50, layers)
+    w = pk.random_weights(cfg, 8)
+    for i, lam in ((2, 0.95), (3, 0.5), (4, 1.0)):
+        w[f"l{i}.mix.vmix"] = torch.tensor(lam).to(torch.bfloat16)
+    w["l1.mix.vmix"] = torch.tensor(0.7).to(torch.bfloat16)      # the first blending layer's own weight is not read
+    write_folder(str(tmp_path), cfg, 0, w)
+    seqs = prompts(cfg, (30, 3, 12), 5)
+    fs = {"blend": (str(tmp_path), cfg, w)}
+    for cut in CUTS + (lambda s: tu.trace_mixed(s, live=3, chunk=4, decode_tail=6),):
+        check_trace(fs, "blend", dtype, cut(seqs), seqs, "blended values")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_tokens(folders, dtype):
+    """Requests of one to five tokens, whole, in portions of one and two, and mixed."""
+    for name in ("all", "ones"):
+        seqs = prompts(CONFIGS[name], (1, 2, 3, 4, 5), 90)
+        check_trace(folders, name, dtype, tu.trace_whole(seqs), seqs, "first tokens")
+        check_trace(folders, name, dtype, tu.trace_chunks(seqs, sizes=(1, 2, 1, 1)), seqs, "first tokens, portions")
+        check_trace(folders, name, dtype, tu.trace_mixed(seqs, live=4, chunk=2, decode_tail=2), seqs, "first tokens, mixed")
+
+
+def test_long_decoding_through_replayed_graphs(folders):
+    name = "all"
+    seqs = prompts(CONFIGS[name], (170, 150), 120)
+    steps = tu.trace_tail_decode(seqs, tail=140)
+    runner = check_trace(folders, name, "float32", steps, seqs, "long decoding")
+    assert runner.graph_replays > 200
+    check_trace(folders, name, "bfloat16", steps, seqs, "long decoding")
+    check_trace(folders, "wide", "bfloat16", steps, prompts(CONFIGS["wide"], (170, 150), 120), "long decoding")
+
+
+@pytest.mark.parametrize("name,dtype,tol", [("all", "float32", 2e-5), ("wide", "float32", 2e-5), ("wide", "bfloat16", 3e-2)])
+def test_a_batch_does_not_change_a_request(folders, name, dtype, tol):
+    """Unequal requests in one step against each alone: equal up to the order of sums."""
+    from sparseengine_b200.engine.runner import StepEntry
+    folder, cfg, w = folders[name]
+    seqs = prompts(cfg, (29, 3, 11), 140)
+    steps = [{"step": 0, "entries": [{"id": sid, "tokens": toks} for sid, toks in seqs.items()], "end": []}]
+    runner = make_runner(folder, dtype, steps, rows=4)       # pages for all three at once
+    alone = {}
+    for sid, toks in seqs.items():
+        runner.admit(sid)
+        runner.step([StepEntry(sid, toks[:-1], [])])
+        alone[sid] = runner.step([StepEntry(sid, toks[-1:], [0])]).float().clone()
+        runner.release(sid)
+    for sid in seqs:
+        runner.admit(sid)
+    runner.step([StepEntry(sid, toks[:-1], []) for sid, toks in seqs.items()])
+    together = runner.step([StepEntry(sid, toks[-1:], [0]) for sid, toks in seqs.items()]).float()
+    for i, sid in enumerate(seqs):
+        assert float((together[i] - alone[sid][0]).abs().max()) < tol * float(alone[sid][0].abs().max()), sid
+
+
+def test_the_stream_after_every_layer(folders):
+    from sparseengine_b200.engine.runner import StepEntry
+    folder, cfg, w = folders["all"]
+    toks = tu.random_prompt(cfg["vocab"], 45, 8)
+    taps = []
+    pk.forward(cfg, w, toks, taps)
+    runner = make_runner(folder, "float32", [{"step": 0, "entries": [{"id": "a", "tokens": toks}], "end": []}])
+    runner.model.stream_taps = got = []
+    runner.admit("a")
+    runner.step([StepEntry("a", toks, [0])])
+    assert len(got) == len(taps) == len(cfg["layers"])
+    for i, (a, b) in enumerate(zip(got, taps)):
+        assert float((a.cpu().double() - b).abs().max()) < 3e-5 * float(b.abs().max()), i
+
+
+# ---- the entry point -----------------------------------------------------------------------------
+
+def plain_greedy(cfg, w, prompt, steps):
+    toks, out, margins = list(prompt), [], []
+    for _ in range(steps):
+        logits = pk.forward(cfg, w, toks)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        out.append(int(logits.argmax()))
+        toks.append(out[-1])
+    return out, margins
+
+
+@pytest.mark.parametrize("name", ["all", "odd"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, cfg, w = folders[name]
+    llm = LLM(folder, dtype="float32", page_size=8, num_kvcache_slots=512, max_num_batched_tokens=16, max_model_len=128,
+              max_num_seqs_in_gpu=3)
+    ps = [tu.random_prompt(cfg["vocab"], n, 200 + n) for n in (5, 21, 9, 2, 14)]
+    outs = llm.generate(ps, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for p, o in zip(ps, outs):
+        want, margins = plain_greedy(cfg, w, p, 10)
+        if min(margins) > 1e-4:
+            assert o["token_ids"] == want
+        else:       # a near-tie: the tokens up to it
+            k = next(i for i, m in enumerate(margins) if m <= 1e-4)
+            assert o["token_ids"][:k] == want[:k]
+    assert llm.is_finished() and llm.runner.cache.free_rows == llm.runner.cache.max_rows
+
+
+def test_trace_program(folders, tmp_path):
+    """bin/trace_run as a program on a folder of this design, pages and rows used again."""
+    name = "wide"
+    folder, cfg, w = folders[name]
+    seqs = prompts(cfg, (40, 7, 22, 31, 3), 300)
+    steps = tu.trace_mixed(seqs, live=4, chunk=9, decode_tail=4)
+    for dtype in ("float32", "bfloat16"):
+        out = str(tmp_path / dtype)
+        got = tu.run_trace_cli(folder, dtype, steps, out, tu.max_live_tokens(steps))
+        worst, where = row_errors(got, plain_logits(name, cfg, w, seqs))
+        assert worst < BOUND[dtype], (dtype, worst, where)
+
+
+def test_temperature_sampling_through_the_entry_point_is_seeded(folders):
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, cfg, w = folders["all"]
+    ps = [tu.random_prompt(cfg["vocab"], n, 400 + n) for n in (3, 17, 8)]
+    kw = dict(dtype="float32", page_size=8, num_kvcache_slots=512, max_model_len=128)
+    sp = SamplingParams(temperature=0.9, top_k=5, max_tokens=8, ignore_eos=True)
+    a = [o["token_ids"] for o in LLM(folder, seed=7, **kw).generate(ps, sp)]
+    b = [o["token_ids"] for o in LLM(folder, seed=7, **kw).generate(ps, sp)]
+    c = [o["token_ids"] for o in LLM(folder, seed=8, **kw).generate(ps, sp)]
+    assert a == b and a != c
+    for p, out in zip(ps, a):
+        toks = list(p)
+        for t in out:       # every sampled token is among the most likely of the plain logits
+            top = torch.topk(pk.forward(cfg, w, toks)[-1], 6).indices.tolist()
+            assert t in top
+            toks.append(t)
+
+
+def test_command_line(folders, tmp_path):
+    import subprocess
+    import sys
+    folder, cfg, w = folders["all"]
+    hyper = json.dumps({"dtype": "bfloat16", "page_size": 8, "num_kvcache_slots": 1024, "max_model_len": 256})
+    for extra in ([], ["--tiny_random"]):
+        r = subprocess.run([sys.executable, "-m", "sparseengine_b200.cli.bench", "--model_path", folder, "--lengths", "24",
+                            "--batch_sizes", "3", "--output_len", "6", "--random_prompts", "--generate", "--hyper_params", hyper,
+                            *extra], cwd=tu.ROOT, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert r.stdout.strip()
