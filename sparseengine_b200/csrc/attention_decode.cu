@@ -152,12 +152,7 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
                 mma_bf16(s[0], qa[kk], b0, b1);
                 mma_bf16(s[1], qa[kk], b2, b3);
             }
-            if (opt.cap_in > 0.f) {
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) s[nt][e] = capped_score(s[nt][e], opt.cap_in, opt.cap_out);
-            }
+            if (opt.cap_in > 0.f) cap_scores<8>(&s[0][0], opt.cap_in, opt.cap_out);
             // mask keys beyond the range (rows share the token, hence the range)
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll

@@ -174,12 +174,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                 mma_bf16(s[2 * n2 + 1], qa[kk], b2, b3);
             }
         }
-        if (opt.cap_in > 0.f) {
-#pragma unroll
-            for (int n = 0; n < kTileKeys / 8; ++n)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[n][e] = capped_score(s[n][e], opt.cap_in, opt.cap_out);
-        }
+        if (opt.cap_in > 0.f) cap_scores<kTileKeys / 2>(&s[0][0], opt.cap_in, opt.cap_out);
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int n = 0; n < kTileKeys / 8; ++n)
@@ -239,6 +234,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
+    const bool gate_vec = opt.gate != nullptr && gate_rows_aligned(opt, 4);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         if (!valid[h]) continue;
@@ -251,8 +247,14 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         for (int i = 0; i < DV / 8; ++i) {
             float a = o[i][2 * h] * inv, b = o[i][2 * h + 1] * inv;
             if (gp != nullptr) {
-                a = gated(a, gp + i * 8 + 2 * t4);
-                b = gated(b, gp + i * 8 + 2 * t4 + 1);
+                if (gate_vec) {       // the thread's two neighbours in one load
+                    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gp + i * 8 + 2 * t4));
+                    a = gated_by(a, g.x);
+                    b = gated_by(b, g.y);
+                } else {
+                    a = gated(a, gp + i * 8 + 2 * t4);
+                    b = gated(b, gp + i * 8 + 2 * t4 + 1);
+                }
             }
             *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = pack_bf16(a, b);
         }

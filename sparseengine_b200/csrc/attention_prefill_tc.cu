@@ -336,9 +336,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(&bars.s_empty[x][b]));
             if (opt.cap_in > 0.f) {
+                // A polynomial form where every score of the warp's 32 x 64 block is small (the warp decides
+                // as one: no divergence), else the exact form with its two more special-function operations.
+                float amax = 0.f;
 #pragma unroll
-                for (int c = 0; c < 64; ++c)
-                    sv[c] = __float_as_uint(se::mma::capped_score(__uint_as_float(sv[c]), opt.cap_in, opt.cap_out));
+                for (int c = 0; c < 64; ++c) amax = fmaxf(amax, fabsf(__uint_as_float(sv[c])));
+                const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));    // non-negative floats order as integers
+                se::mma::cap_scores_by<64>(reinterpret_cast<float*>(sv), __uint_as_float(wmax) * opt.cap_in, opt.cap_in, opt.cap_out);
             }
             const int key0 = k_begin + j * kKeys;
             // A tile every row of the warp sees in full needs no masking (rows ascend with the
@@ -418,6 +422,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             if (opt.sink) l += exp2f(-m_ref);
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D;
+            const bool gate_vec = opt.gate != nullptr && se::mma::gate_rows_aligned(opt, 16);
             const __nv_bfloat16* gp = opt.gate != nullptr
                 ? opt.gate + (size_t)(tok0 + rr / group) * opt.gate_pitch + (size_t)(kvh * group + rr % group) * D : nullptr;
 #pragma unroll 1
@@ -429,12 +434,21 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
+                        uint4 graw = make_uint4(0u, 0u, 0u, 0u);           // eight gate values in one load where the rows allow it
+                        if (gp != nullptr && gate_vec) graw = *reinterpret_cast<const uint4*>(gp + c0 + c);
+                        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             float a = __uint_as_float(ov[c + 2 * i]) * inv, b = __uint_as_float(ov[c + 2 * i + 1]) * inv;
                             if (gp != nullptr) {
-                                a = se::mma::gated(a, gp + c0 + c + 2 * i);
-                                b = se::mma::gated(b, gp + c0 + c + 2 * i + 1);
+                                if (gate_vec) {
+                                    const float2 g = __bfloat1622float2(g2[i]);
+                                    a = se::mma::gated_by(a, g.x);
+                                    b = se::mma::gated_by(b, g.y);
+                                } else {
+                                    a = se::mma::gated(a, gp + c0 + c + 2 * i);
+                                    b = se::mma::gated(b, gp + c0 + c + 2 * i + 1);
+                                }
                             }
                             w[i] = se::mma::pack_bf16(a, b);
                         }

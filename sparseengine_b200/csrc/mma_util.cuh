@@ -62,8 +62,84 @@ __device__ __forceinline__ float capped_score(float s, float cap_in, float cap_o
     const float x = fminf(fmaxf(s * cap_in, -15.f), 15.f);
     return cap_out * (1.f - __fdividef(2.f, __expf(2.f * x) + 1.f));
 }
+// Two 32-bit products or fused multiply-adds in one instruction (sm_100: `mul.rn.f32x2`, `fma.rn.f32x2`).
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return reinterpret_cast<float2&>(d);
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(reinterpret_cast<unsigned long long&>(a)),
+        "l"(reinterpret_cast<unsigned long long&>(b)), "l"(reinterpret_cast<unsigned long long&>(c)));
+    return reinterpret_cast<float2&>(d);
+}
+// The cap without the special-function unit, two scores at a time: with x = s * cap_in,
+// cap_out * tanh(x) = s * P(x^2) since cap_in * cap_out = 1 and tanh(x) = x P(x^2).  WIDE = false: P of degree 4,
+// fitted on |x| <= 0.5; WIDE = true: degree 7, on |x| <= 1 (relative error 1.0e-7 and 1.2e-7 when evaluated in
+// 32-bit).  Scores of a model are mostly far inside its cap, and the softmax warps of the tensor-core prompt kernel
+// have no time to spare: their exponentials alone keep the special-function unit as busy as the matrix products keep
+// the tensor cores.
+template <bool WIDE>
+__device__ __forceinline__ float2 capped_pair_small(float2 s, float cap_in) {
+    const float2 x = mul2(s, make_float2(cap_in, cap_in));
+    const float2 t = mul2(x, x);
+    float2 p;
+#define SE_C2(v) make_float2(v, v)
+    if (WIDE) {
+        p = fma2(SE_C2(-0.0003548834065441042f), t, SE_C2(0.0022876455914229155f));
+        p = fma2(p, t, SE_C2(-0.007924946025013924f));
+        p = fma2(p, t, SE_C2(0.021469980478286743f));
+        p = fma2(p, t, SE_C2(-0.053872738033533096f));
+        p = fma2(p, t, SE_C2(0.13332191109657288f));
+        p = fma2(p, t, SE_C2(-0.3333328068256378f));
+    } else {
+        p = fma2(SE_C2(0.01723547652363777f), t, SE_C2(-0.0530422069132328f));
+        p = fma2(p, t, SE_C2(0.13325822353363037f));
+        p = fma2(p, t, SE_C2(-0.3333314061164856f));
+    }
+    p = fma2(p, t, SE_C2(1.f));
+#undef SE_C2
+    return mul2(s, p);
+}
+// N scores of a thread (N even), given the largest |s * cap_in| among them (or among a group of threads that
+// decides as one): the short polynomial, the long one, or the exact form for all.
+template <int N>
+__device__ __forceinline__ void cap_scores_by(float* s, float xmax, float cap_in, float cap_out) {
+    if (xmax <= 0.5f) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const float2 r = capped_pair_small<false>(make_float2(s[i], s[i + 1]), cap_in);
+            s[i] = r.x; s[i + 1] = r.y;
+        }
+    } else if (xmax <= 1.f) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const float2 r = capped_pair_small<true>(make_float2(s[i], s[i + 1]), cap_in);
+            s[i] = r.x; s[i + 1] = r.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) s[i] = capped_score(s[i], cap_in, cap_out);
+    }
+}
+template <int N>
+__device__ __forceinline__ void cap_scores(float* s, float cap_in, float cap_out) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) amax = fmaxf(amax, fabsf(s[i]));
+    cap_scores_by<N>(s, amax * cap_in, cap_in, cap_out);
+}
+__device__ __forceinline__ float gated_by(float o, float g) {
+    return __fdividef(o, 1.f + __expf(-g));
+}
 __device__ __forceinline__ float gated(float o, const __nv_bfloat16* gate) {
-    return o / (1.f + __expf(-__bfloat162float(*gate)));
+    return gated_by(o, __bfloat162float(*gate));
+}
+// Whether the gate's rows can be read 16 bytes (8 elements) or 4 bytes (2 elements) at a time, for head
+// sizes that are multiples of 8.
+__device__ __forceinline__ bool gate_rows_aligned(const SoftmaxOptions& opt, int bytes) {
+    return (reinterpret_cast<uintptr_t>(opt.gate) & (bytes - 1)) == 0 && (opt.gate_pitch * 2) % bytes == 0;
 }
 
 }  // namespace mma

@@ -19,6 +19,8 @@
 
 namespace se {
 
+constexpr int kMaxHalf = 128;       // half of the largest rotated width (head sizes up to 256)
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 qk_prep_general_kernel(const T* proj, int pitch, const T* __restrict__ q_w, const T* __restrict__ k_w,
@@ -42,18 +44,109 @@ qk_prep_general_kernel(const T* proj, int pitch, const T* __restrict__ q_w, cons
     float temp = 1.f;
     if (temp_coef != 0.f && temp_every > 0) temp = 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
     const T* row = proj + (size_t)t * pitch;
-    float inv_q = 1.f, inv_k = 1.f;
-    if (q_w != nullptr) {
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < qn; i += blockDim.x) { const float v = to_float(row[i]); ss += v * v; }
-        inv_q = 1.0f / sqrtf(block_sum(ss, scratch) / (float)qn + eps);
-    }
-    if (k_w != nullptr && has_kv) {
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < kn; i += blockDim.x) { const float v = to_float(row[qn + i]); ss += v * v; }
-        inv_k = 1.0f / sqrtf(block_sum(ss, scratch) / (float)kn + eps);
-    }
     const int half = rotary_dim / 2;
+    const T* vf = v_first != nullptr ? v_first + (size_t)t * v_first_pitch : nullptr;
+    // Eight elements at a time where sizes and addresses allow it.
+    const bool vec = (d & 7) == 0 && (half & 7) == 0 && (dv & 7) == 0 && (pitch & 7) == 0 && aligned8(proj) && aligned8(q_out) &&
+                     (q_w == nullptr || aligned8(q_w)) && (k_w == nullptr || aligned8(k_w)) && (cache == nullptr || aligned8(cache)) &&
+                     (vf == nullptr || ((v_first_pitch & 7) == 0 && aligned8(v_first)));
+    auto sum_squares = [&](const T* part, int n) {
+        float ss = 0.f;
+        if (vec) {
+            for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+                float v[8];
+                load8(part + i, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+            }
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_float(part[i]); ss += v * v; }
+        }
+        return block_sum(ss, scratch);
+    };
+    float inv_q = 1.f, inv_k = 1.f;
+    if (q_w != nullptr) inv_q = 1.0f / sqrtf(sum_squares(row, qn) / (float)qn + eps);
+    if (k_w != nullptr && has_kv) inv_k = 1.0f / sqrtf(sum_squares(row + qn, kn) / (float)kn + eps);
+    // cos and sin of the token's angles, once for all heads
+    __shared__ float cs_t[kMaxHalf], sn_t[kMaxHalf];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn_t[i], &cs_t[i]);
+    __syncthreads();
+    T* kbase = nullptr;
+    T* vbase = nullptr;
+    if (has_kv) {
+        const size_t page_elems = (size_t)hkv * page_size * (d + dv);
+        kbase = cache + (size_t)page * page_elems + (size_t)(pos % page_size) * d;
+        vbase = cache + (size_t)page * page_elems + (size_t)hkv * page_size * d + (size_t)(pos % page_size) * dv;
+    }
+    const float mix = v_first != nullptr ? v_mix[0] : 0.f;
+    T* qdst = q_out + (size_t)t * qn;
+
+    // The 8-wide path: a work item is a pair of 8-element chunks that rotate into one another (columns c
+    // and c + half of a head), or one chunk that passes.
+    if (vec) {
+        const int pair_items = half / 8, items = d / 8 - pair_items;          // per head
+        auto normed8 = [&](const T* part, const T* w, float inv, int i, float* v) {
+            load8(part + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] *= inv;
+            if (w != nullptr) {
+                float ww[8];
+                load8(w + i, ww);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= ww[j];
+            }
+        };
+        // heads of the queries, then (with keys) heads of the keys
+        const int heads = hq + (has_kv ? hkv : 0);
+        for (int it = threadIdx.x; it < heads * items; it += blockDim.x) {
+            const int h = it / items, k = it - h * items;
+            const bool is_q = h < hq;
+            const int hh = is_q ? h : h - hq;
+            const T* part = is_q ? row : row + qn;
+            const T* w = is_q ? q_w : k_w;
+            const float inv = is_q ? inv_q : inv_k, mul = is_q ? temp : 1.f;
+            T* dst = is_q ? qdst + (size_t)hh * d : kbase + (size_t)hh * page_size * d;
+            float a[8];
+            if (k < pair_items) {
+                const int c = k * 8;
+                float b[8], ra[8], rb[8];
+                normed8(part, w, inv, hh * d + c, a);
+                normed8(part, w, inv, hh * d + c + half, b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float cs = cs_t[c + j], sn = sn_t[c + j];
+                    ra[j] = (a[j] * cs - b[j] * sn) * mul;
+                    rb[j] = (b[j] * cs + a[j] * sn) * mul;
+                }
+                store8(dst + c, ra);
+                store8(dst + c + half, rb);
+            } else {
+                const int c = rotary_dim + (k - pair_items) * 8;
+                normed8(part, w, inv, hh * d + c, a);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] *= mul;
+                store8(dst + c, a);
+            }
+        }
+        if (!has_kv) return;
+        for (int i = threadIdx.x * 8; i < vn; i += blockDim.x * 8) {
+            const int h = i / dv, c = i - h * dv;
+            if (vf == nullptr) {
+                *reinterpret_cast<uint4*>(vbase + (size_t)h * page_size * dv + c) = *reinterpret_cast<const uint4*>(row + qn + kn + i);
+                if (sizeof(T) == 4)
+                    *reinterpret_cast<uint4*>(vbase + (size_t)h * page_size * dv + c + 4) = *reinterpret_cast<const uint4*>(row + qn + kn + i + 4);
+            } else {
+                float a[8], f[8];
+                load8(row + qn + kn + i, a);
+                load8(vf + i, f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] = (1.f - mix) * a[j] + mix * f[j];
+                store8(vbase + (size_t)h * page_size * dv + c, a);
+            }
+        }
+        return;
+    }
+
     // element i of a projection part (norm weights w, inverse root mean square inv), normed and rotated
     auto prepared = [&](const T* part, const T* w, float inv, int i) {
         float v = to_float(part[i]) * inv;
@@ -63,26 +156,20 @@ qk_prep_general_kernel(const T* proj, int pitch, const T* __restrict__ q_w, cons
         const int j = c < half ? i + half : i - half;
         float u = to_float(part[j]) * inv;
         if (w != nullptr) u *= to_float(w[j]);
-        float sn, cs;
-        sincosf((float)pos * inv_freq[c < half ? c : c - half], &sn, &cs);
+        const float sn = sn_t[c < half ? c : c - half], cs = cs_t[c < half ? c : c - half];
         return c < half ? v * cs - u * sn : v * cs + u * sn;
     };
     for (int i = threadIdx.x; i < qn; i += blockDim.x)
-        q_out[(size_t)t * qn + i] = from_float<T>(prepared(row, q_w, inv_q, i) * temp);
+        qdst[i] = from_float<T>(prepared(row, q_w, inv_q, i) * temp);
     if (!has_kv) return;
-    const size_t page_elems = (size_t)hkv * page_size * (d + dv);
-    T* kbase = cache + (size_t)page * page_elems + (size_t)(pos % page_size) * d;
-    T* vbase = cache + (size_t)page * page_elems + (size_t)hkv * page_size * d + (size_t)(pos % page_size) * dv;
     for (int i = threadIdx.x; i < kn; i += blockDim.x) {
         const int h = i / d, c = i - h * d;
         kbase[(size_t)h * page_size * d + c] = from_float<T>(prepared(row + qn, k_w, inv_k, i));
     }
-    const float mix = v_first != nullptr ? v_mix[0] : 0.f;
     for (int i = threadIdx.x; i < vn; i += blockDim.x) {
         const int h = i / dv, c = i - h * dv;
         T v = row[qn + kn + i];
-        if (v_first != nullptr)
-            v = from_float<T>((1.f - mix) * to_float(v) + mix * to_float(v_first[(size_t)t * v_first_pitch + i]));
+        if (vf != nullptr) v = from_float<T>((1.f - mix) * to_float(v) + mix * to_float(vf[i]));
         vbase[(size_t)h * page_size * dv + c] = v;
     }
 }
@@ -100,6 +187,7 @@ extern "C" int se_qk_prep_general(const void* proj, int pitch, const void* q_w, 
     if (hq <= 0 || d <= 0 || (has_kv && (hkv <= 0 || dv <= 0 || page_size <= 0))) return SE_ERR_ARGUMENT;
     if (pitch < hq * d + (has_kv ? hkv * (d + dv) : 0)) return SE_ERR_ARGUMENT;
     if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr)) return SE_ERR_ARGUMENT;
+    if (rotary_dim > 2 * se::kMaxHalf) return SE_ERR_UNSUPPORTED;
     if (v_first != nullptr && (v_mix == nullptr || !has_kv || v_first_pitch < hkv * dv)) return SE_ERR_ARGUMENT;
     SE_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e = SE_LAUNCH_DEPENDENT("qk", se::qk_prep_general_kernel<T>, dim3(tokens), dim3(256), 0, stream,

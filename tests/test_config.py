@@ -128,7 +128,7 @@ def test_scaled_rotary_tables_are_built_on_the_host_and_match_the_reference():
     assert load_model_spec(typed.to_dict())[0] == typed                 # and reads back from its own config.json
     for bad in ({"rope_type": "dynamic", "factor": 2.0}, {"rope_type": "yarn", "factor": 2.0},
                 {"rope_type": "llama3", "factor": 2.0, "original_max_position_embeddings": 64, "low_freq_factor": 4.0,
-                 "high_freq_factor": 1.0}, {"rope_type": "linear", "factor": 0.5}):
+                 "high_freq_factor": 1.0}, {"rope_type": "linear", "factor": 0.0}):
         with pytest.raises(ValueError):
             load_model_spec(dict(plain_m2.TINY_A, rope_scaling=bad))
     with pytest.raises(ValueError):
