@@ -33,8 +33,8 @@ def kisusun_config(width: int, layers: int = LAYERS) -> dict:
     the others route 2 of 8 experts of ``width`` each in 4 groups of which 2 stay open, plus a shared
     expert of ``width``: three experts' worth of active feed-forward weights per token and layer."""
     heads = width // 128
-    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
-             "mask": {"size": WINDOW}, "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0}}, "v_mix": True}
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+             "mask": {"size": WINDOW}, "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 8.0}}, "v_mix": True}
     moe = {"kind": "moe", "expert": {"ff": width, "limit": 7.0},
            "router": {"experts": EXPERTS, "top": 2, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
            "shared": {"ff": width, "limit": 7.0}}
@@ -101,7 +101,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
         v_first = torch.randn(tokens, kn, device=dev, dtype=bf)
         mix = torch.full((), 0.3, device=dev)
         qw, kw = torch.ones(qn, device=dev, dtype=bf), torch.ones(kn, device=dev, dtype=bf)
-        inv = (1e6 ** (-torch.arange(0, 64, 2, dtype=torch.float32) / 64) / 4.0).to(dev)
+        inv = (1e6 ** (-torch.arange(0, 64, 2, dtype=torch.float32) / 64) / 8.0).to(dev)
         qo = torch.empty(tokens, qn, device=dev, dtype=bf)
         add("qk_prep_general (rotation, blended values)", lambda: ops.qk_prep_general(
             proj, qw, kw, step.positions, step.token_seq, step.seq_rows, table, cache, qo, num_heads=hq, num_kv_heads=hkv,
@@ -115,7 +115,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
         q = torch.randn(tokens, qn, device=dev, dtype=bf)
         o = torch.empty(tokens, qn, device=dev, dtype=bf)
         gate = proj[:, qn + 2 * kn:]
-        opts = dict(softcap=30.0, sink=True, gate=gate)
+        opts = dict(softcap=50.0, sink=True, gate=gate)
         seen = sum(min(WINDOW, held + i + 1) for i in range(per)) * entries
         key_rows = entries * min(held + per, WINDOW + per - 1)
         if per > 1:
@@ -149,7 +149,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
             common = dict(entries=entries, max_q_len=per, num_heads=h64, num_kv_heads=g64, head_dim=64, page_size=PAGE_SIZE,
                           scale=0.125, window=WINDOW)
             add("attn_prefill (heads of 64, values of 32; cap, sink, gate)", lambda: ops.attn_prefill(
-                q64, cache64, table, step.seq_rows, step.cu_q, kv_len, o64, v_head_dim=32, softcap=30.0, sink=True, gate=gate64, **common),
+                q64, cache64, table, step.seq_rows, step.cu_q, kv_len, o64, v_head_dim=32, softcap=50.0, sink=True, gate=gate64, **common),
                 flops=2.0 * seen * h64 * 96)
             add("like: attn_prefill (heads of 64)", lambda: ops.attn_prefill(q64, cache6464, table, step.seq_rows, step.cu_q, kv_len,
                                                                             o6464, **common), flops=4.0 * seen * h64 * 64)
@@ -157,7 +157,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
             common = dict(num_heads=h64, num_kv_heads=g64, head_dim=64, page_size=PAGE_SIZE, scale=0.125, window=WINDOW,
                           max_keys=min(WINDOW, held + 1))
             add("attn_decode (heads of 64, values of 32; cap, sink, gate)", lambda: ops.attn_decode(
-                q64, cache64, table, step.seq_rows, step.token_seq, step.positions, o64, v_head_dim=32, softcap=30.0, sink=True,
+                q64, cache64, table, step.seq_rows, step.token_seq, step.positions, o64, v_head_dim=32, softcap=50.0, sink=True,
                 gate=gate64, **common), nbytes=key_rows * g64 * 96 * 2 + tokens * h64 * (64 + 32 + 32) * 2)
             add("like: attn_decode (heads of 64)", lambda: ops.attn_decode(
                 q64, cache6464, table, step.seq_rows, step.token_seq, step.positions, o6464, **common),
