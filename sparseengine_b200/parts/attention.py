@@ -129,7 +129,9 @@ class PagedAttention(Mixer):
         if s.output_gate:
             g0 = q_cols + (kv_cols + v_cols if s.own_kv else 0)
             gate = proj[:, g0:g0 + s.num_heads * s.value_dim]
-        self.attend(q, attn, step, slot, gate=gate)
+        # the kernel before the attention is the one that wrote q and this step's keys; it waited for the
+        # projection (whose columns the gate is), and the step's inputs are older than both
+        self.attend(q, attn, step, slot, after_qk_prep=True, gate=gate)
         return linear(attn, self.o)
 
     def forward(self, x, step, slot):

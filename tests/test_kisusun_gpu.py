@@ -276,6 +276,29 @@ def test_grouped_selection_alone():
     assert 0 not in pk.route(logits.double(), w, "", router)[0][0].tolist()
 
 
+@pytest.mark.parametrize("impl", ["block", "warp"])
+def test_grouped_selection_of_many_experts(impl):
+    """Random logits, many experts, both forms of the selection kernel, against the plain routing; rows
+    in which the plain routing made a close call are left out."""
+    from sparseengine_b200.csrc import ops
+    g = torch.Generator().manual_seed(17)
+    for experts, count, keep, top in ((6, 3, 2, 2), (12, 4, 2, 4), (64, 8, 4, 6), (128, 8, 2, 8), (256, 16, 3, 5), (20, 1, 1, 7), (30, 30, 9, 3)):
+        logits = torch.randn(200, experts, generator=g) * 1.5
+        router = {"experts": experts, "top": top, "scale": 0.75, "groups": {"count": count, "keep": keep}}
+        margins = []
+        want_ids, want_w = pk.route(logits.double(), {"router": torch.eye(experts, dtype=torch.float64)}, "", router, margins)
+        clear = torch.stack(margins).min(0).values > 1e-5 if margins else torch.ones(200, dtype=torch.bool)
+        assert int(clear.sum()) > 190
+        ids = torch.empty(200, top, dtype=torch.int32, device=DEV)
+        wt = torch.empty(200, top, dtype=torch.float32, device=DEV)
+        ops.router_select(logits.to(DEV), None, ids, wt, top_k=top, score_fn="sigmoid", renormalize=False, routed_scale=0.75,
+                          impl=impl, groups=count, keep_groups=keep)
+        got = torch.zeros(200, experts).scatter_(1, ids.cpu().long(), wt.cpu())
+        ref = torch.zeros(200, experts, dtype=torch.float64).scatter_(1, want_ids, want_w)
+        assert torch.equal(ids.cpu().long().sort(-1).values[clear], want_ids.sort(-1).values[clear]), (experts, count, keep, top)
+        assert float((got.double() - ref)[clear].abs().max()) < 1e-5, (experts, count, keep, top)
+
+
 def test_clamped_expert_alone():
     """The experts' gated activation with its clamps against the plain form, through the feed-forward
     part of the engine (one expert that every token uses), at pre-activations far outside the limit."""
