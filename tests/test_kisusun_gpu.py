@@ -291,8 +291,13 @@ def test_grouped_selection_of_many_experts(impl):
         assert int(clear.sum()) > 190
         ids = torch.empty(200, top, dtype=torch.int32, device=DEV)
         wt = torch.empty(200, top, dtype=torch.float32, device=DEV)
-        ops.router_select(logits.to(DEV), None, ids, wt, top_k=top, score_fn="sigmoid", renormalize=False, routed_scale=0.75,
-                          impl=impl, groups=count, keep_groups=keep)
+        call = lambda: ops.router_select(logits.to(DEV), None, ids, wt, top_k=top, score_fn="sigmoid", renormalize=False,
+                                         routed_scale=0.75, impl=impl, groups=count, keep_groups=keep)
+        if impl == "warp" and count > 1:        # groups are the block kernel's; asked of the other by name, they are refused
+            with pytest.raises(ValueError):
+                call()
+            continue
+        call()
         got = torch.zeros(200, experts).scatter_(1, ids.cpu().long(), wt.cpu())
         ref = torch.zeros(200, experts, dtype=torch.float64).scatter_(1, want_ids, want_w)
         assert torch.equal(ids.cpu().long().sort(-1).values[clear], want_ids.sort(-1).values[clear]), (experts, count, keep, top)
