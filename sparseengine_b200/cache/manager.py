@@ -9,7 +9,8 @@ pages per kind of layer, and fixed-size per-request state slots.
   ``i*page_size .. (i+1)*page_size-1`` in every cache layer of the group.
 * A request is **admitted** (gets a row and zeroed state slots), **reserves** pages for
   its next tokens before a step (all groups or none), **commits** them after the step
-  (a windowed group then gives back the pages no later query can see) and is
+  (a windowed group then gives back the pages no later query can see; pages that hold the first
+  ``keep_first`` positions of a group that keeps them are never given back early) and is
   **released** when it ends (everything returns to the pools).
 * **State slots**: ``state[i][row]`` is a tensor of fixed shape per request for schedule
   entries whose mixer declared a :class:`StateRequest`.  The dense-cache attention of
@@ -204,7 +205,9 @@ class CacheManager:
             if g.window is None:
                 continue
             first_needed = max(0, r.length - g.window + 1)     # the next query's oldest key
-            dead = [idx for idx in r.pages[gi] if (idx + 1) * self.page_size <= first_needed]
+            keep = getattr(g.request, "keep_first", 0)         # positions below it stay visible to every later query
+            dead = [idx for idx in r.pages[gi] if (idx + 1) * self.page_size <= first_needed
+                    and idx * self.page_size >= keep]
             if dead:
                 g.pool.give([r.pages[gi].pop(idx) for idx in dead])
                 for idx in dead:

@@ -234,7 +234,7 @@ def _kernels(width: int, tokens_list, pk: dict) -> dict:
             tokens * (C + H * d + H * dv) * 4 + entries * H * d * dv * 8, iters=5)
         rec["delta_scan"]["us_per_token_of_a_request"] = round(rec["delta_scan"]["us"] / per, 3)
         gate, nw2, out2 = torch.randn(tokens, H * dv, device=dev, dtype=bf), torch.ones(dv, device=dev), torch.empty(tokens, H * dv, device=dev, dtype=bf)
-        add("delta_out", lambda: ops.delta_out(oo2, gate, nw2, out2, v_head_dim=dv, eps=1e-6), tokens * H * dv * 8)
+        add("delta_out", lambda: ops.delta_out(oo2, gate, nw2, out2, heads=H, v_head_dim=dv, eps=1e-6), tokens * H * dv * 8)
         # query/key preparation (pages written round-robin)
         kvh = max(1, heads // 4)
         qn, kn = heads * 128, kvh * 128

@@ -64,6 +64,9 @@ class RMSNormSpec:
     kind: str = "rms"
     size: int = 0
     eps: float = 1e-6
+    # the stored weight w is applied as (offset + w): 1.0 for weights kept around zero.  Such a norm keeps its
+    # weight in 32-bit (the sum would lose the stored digits in a 16-bit type).
+    offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -84,7 +87,9 @@ class AttentionSpec:
     num_kv_heads: int = 0
     head_dim: int = 0
     scale: float = 1.0
-    qk_norm: Optional[str] = None     # None | "whole_projection"
+    # None | "whole_projection" (one root mean square over all heads, a weight per column) | "per_head" (one per
+    # head, a weight of head_dim elements shared by the heads; needs prep="general")
+    qk_norm: Optional[str] = None
     qk_norm_eps: float = 1e-6
     window: Optional[int] = None      # keys p-window+1..p; None = all keys
     position: Optional[Any] = None    # a position-encoding spec (e.g. RotarySpec)
@@ -97,8 +102,15 @@ class AttentionSpec:
     own_kv: bool = True               # False: no key/value projections; the layer attends over another's cache
     # The fields below need prep="general", which then also rotates (``position``: split halves, no factor).
     score_softcap: Optional[float] = None   # c: the scaled score becomes c * tanh(score / c)
-    # "zero": a key of score 0 that has no value joins the softmax: p_j = exp(s_j) / (1 + sum exp(s_j))
+    # "zero": a key of score 0 that has no value joins the softmax: p_j = exp(s_j) / (1 + sum exp(s_j)).
+    # "learned": the same with a learned logit per head (parameter ``sink``) in place of 0, unscaled.
     sink: Optional[str] = None
+    # with a window: the first keep_first positions stay visible to every later query (at their true positions),
+    # beside the window's keys
+    keep_first: int = 0
+    # biases on the q, k, v rows of the packed projection (parameter ``qkv_bias``) and on the output projection
+    # (``o_bias``); needs prep="general"
+    bias: bool = False
     # the concatenated heads are multiplied by sigmoid(W_g x) before the output projection; W_g's
     # rows follow the values' in the packed projection
     output_gate: bool = False
@@ -130,9 +142,11 @@ class StateSpaceSpec:
 
 @dataclass(frozen=True)
 class GatedDeltaSpec:
-    """Gated delta rule with one decay per head and key channel: per head a state of
-    ``head_dim x v_head_dim``; q, k, v through short causal convolutions; the decay and the output
-    gate come through low-rank projections of the given ranks."""
+    """Gated delta rule: per head a state of ``head_dim x v_head_dim``; q, k, v through short causal
+    convolutions.  ``decay_per="channel"``: one decay per head and key channel; the decay and the output
+    gate come through low-rank projections of the given ranks, the gate is a sigmoid.
+    ``decay_per="head"``: one decay per head, straight from a projection of the input (no ranks); the
+    output gate is ``gate_activation`` of a full projection."""
     kind: str = "channel_delta"
     hidden_size: int = 0
     num_heads: int = 0
@@ -144,6 +158,51 @@ class GatedDeltaSpec:
     gate_rank: int = 0
     norm_eps: float = 1e-6
     unit_eps: float = 1e-6            # q and k become x / sqrt(sum(x^2) + unit_eps)
+    decay_per: str = "channel"        # "channel" | "head"
+    gate_activation: str = "sigmoid"  # "sigmoid" | "silu" (of the output gate)
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """Matrix memory with exponential gates (the mLSTM cell): per head a state ``S [head_dim, v_head_dim]``, a
+    vector ``n [head_dim]`` and a running maximum ``m`` of the gates' logarithms, all starting at 0.  With
+    ``i = cap tanh(a / cap)`` and ``f = logsigmoid(cap tanh(b / cap))`` (a, b: projections with bias, one per
+    head): ``m' = max(f + m, i)``, ``S' = exp(f + m - m') S + exp(i - m') k v^T``, ``n'`` likewise with k alone,
+    ``o = S'^T q / (max(|n' . q|, exp(-m')) + den_eps)`` with ``q`` scaled by ``head_dim ** -0.5``.  Each head's
+    ``o`` is divided by its root mean square, the concatenated heads are multiplied by a weight and by
+    ``sigmoid(W_g x)``, then projected."""
+    kind: str = "matrix_memory"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    gate_cap: float = 15.0
+    norm_eps: float = 1e-6
+    den_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Mixers side by side on the same input: the result is ``sum_i scales[i] * branch_i(x)``.  At most one
+    branch may ask for pages and at most one for a state slot."""
+    kind: str = "parallel"
+    hidden_size: int = 0
+    branches: tuple = ()              # mixer specs
+    scales: tuple = ()                # one factor per branch
+    names: tuple = ()                 # a name per branch: its parameters are "<name>_<parameter>"
+
+
+@dataclass(frozen=True)
+class StreamMixSpec:
+    """How one sublayer reads from and writes to ``streams`` copies of the residual stream
+    (hyper-connections): it reads ``sum_s in[s] x_s`` and writes ``x_t <- sum_s mix[s, t] x_s + out[t] y``.
+    ``gated``: ``y`` is first multiplied by ``sigmoid(W h + b)``, ``h`` being the sublayer's (normed) input.
+    ``learned=False`` (one stream only): in, out and mix are 1, the plain residual sum."""
+    kind: str = "stream_mix"
+    hidden_size: int = 0
+    streams: int = 1
+    gated: bool = False
+    learned: bool = True
 
 
 @dataclass(frozen=True)
@@ -212,6 +271,9 @@ class MoESpec:
     keep_groups: int = 1
     # a DenseMLPSpec: an expert of its own sizes that every token runs; its output is added
     shared: Optional[Any] = None
+    # the router has this many more outputs after the experts': "experts" without weights whose output is
+    # their input; they take part in scores and selection like the others
+    identity_experts: int = 0
 
 
 @dataclass(frozen=True)
@@ -252,6 +314,8 @@ class LayerSpec:
     # feed-forward (with its norm) may be None.
     # "post_norm": x <- norm(residual_scale * x + sublayer(x)) for each sublayer; the feed-forward
     # (with its norm) may be None
+    # "stream_mix": pre-norm over several 32-bit streams; extra["mixer_streams"] and extra["feed_forward_streams"]
+    # (StreamMixSpec) say how each sublayer reads and writes them; the feed-forward may be None.
     # "sublayer_norm": x <- x + norm(mixer(x)), x <- x + norm(ff(x)) over a 32-bit stream: the norms
     # sit on the sublayers' outputs and the sublayers read x itself; the feed-forward (with its
     # norm) may be None
@@ -304,3 +368,4 @@ class ModelSpec:
     # the stream), the embedding is scaled in 32-bit and the final norm reads the stream.
     residual_stream: str = "activation"
     reinject_source: Optional[str] = None           # checkpoint name of the [width, 2 width] matrix of ScheduleEntry.reinject
+    streams: int = 1                                # copies of the residual stream ("stream_mix" blocks); the last norm reads their sum

@@ -12,7 +12,7 @@
 // 32-bit, probabilities rounded to bfloat16 before they multiply V, the output rounded once.
 //
 // Any page size; query/key head sizes 64 and 128, value head sizes 32, 64 and 128 (others use the
-// plain kernel); a window is honoured.  A page holds the keys [kv head][slot][D] and then the values
+// plain kernel); a window is honoured, with or without first keys that stay visible.  A page holds the keys [kv head][slot][D] and then the values
 // [kv head][slot][DV].  The softmax's options (a cap on the scores, a sink of score 0, an output gate)
 // are those of mma_util.cuh's SoftmaxOptions; the sink joins once, where the last sum is taken (here
 // for one split, in the second kernel for several), and the gate where the output is rounded.
@@ -55,9 +55,13 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
     const int g = lane >> 2, t4 = lane & 3;
 
     const int pos = positions[t];
+    // The keys a token sees, in the order they are visited: the kept first ones that lie before the window,
+    // then the window's.  ks, ke and the tiles count in that order; key_of gives a place's position.
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int ks = lo + split * keys_per_split;
-    const int ke = min(pos + 1, ks + keys_per_split);
+    const int kept = min(opt.keep_first, lo);
+    const int ks = split * keys_per_split;
+    const int ke = min(kept + pos + 1 - lo, ks + keys_per_split);
+    auto key_of = [&](int n) { return n < kept ? n : lo + n - kept; };
     const int* row_table = table + (size_t)seq_rows[token_seq[t]] * table_stride;
     const size_t page_elems = (size_t)hkv * page_size * (D + DV);
     const size_t head_off = (size_t)kvh * page_size * D;
@@ -84,7 +88,7 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
 #pragma unroll
         for (int k = 0; k < kIters; ++k) {
             const int j = base + r0t + k * kRowStep;
-            const int jj = j < ke ? j : ks;      // any valid key: the copy is zero-filled when out of range
+            const int jj = key_of(j < ke ? j : ks);      // any valid key: the copy is zero-filled when out of range
             const int page = row_table[jj / page_size];
             // an entry that names no page of the pool is not followed: its rows are zero-filled
             page_ok[k] = page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_DECODE);
@@ -244,7 +248,7 @@ attn_decode_kernel(const __nv_bfloat16* q, const __nv_bfloat16* cache,      // w
         const int head = head0 + r;
         if (splits == 1) {
             // the sink's term 2^(0 - mt): it grows beyond the type only where the keys hold nothing (the output is 0 then)
-            if (opt.sink) lt += exp2f(-mt * scale_log2);
+            if (opt.sink) lt += exp2f(sink_log2(opt, head) - mt * scale_log2);
             float v = acc / lt;
             if (opt.gate != nullptr) v = gated(v, opt.gate + (size_t)t * opt.gate_pitch + (size_t)head * DV + d);
             out[((size_t)t * hq + head) * DV + d] = __float2bfloat16_rn(v);
@@ -275,7 +279,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
             acc += part_o[(th * splits + s) * d + i] * f;
             lt += part_ml[(th * splits + s) * 2 + 1] * f;
         }
-        if (opt.sink) lt += exp2f(-mt);
+        if (opt.sink) lt += exp2f(sink_log2(opt, (int)(th % hq)) - mt);
         float v = acc / lt;
         if (opt.gate != nullptr) v = gated(v, opt.gate + (th / hq) * opt.gate_pitch + (th % hq) * d + i);
         out[th * d + i] = __float2bfloat16_rn(v);
@@ -335,15 +339,17 @@ extern "C" int se_attn_decode(const void* q, const void* cache, const int* table
                               float* part_o, float* part_ml, int tokens, int hq, int hkv, int head_dim, int v_head_dim,
                               int page_size, float scale, int window, int splits, int keys_per_split, int num_pages,
                               int* error, int settled, float softcap, int sink, const void* gate, int gate_pitch,
-                              cudaStream_t stream) {
+                              const float* sink_logits, int keep_first, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (!se_attn_decode_supported(head_dim, hq, hkv) || !se_attn_decode_value_dim_supported(v_head_dim) || splits < 1 ||
         keys_per_split <= 0 || keys_per_split % 64)
         return SE_ERR_UNSUPPORTED;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
-    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * v_head_dim)) return SE_ERR_ARGUMENT;
-    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink,
-                                      (const __nv_bfloat16*)gate, gate_pitch};
+    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * v_head_dim) || keep_first < 0)
+        return SE_ERR_ARGUMENT;
+    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f,
+                                      sink || sink_logits != nullptr, (const __nv_bfloat16*)gate, gate_pitch, sink_logits,
+                                      window > 0 ? keep_first : 0};
 #define SE_DECODE_CASE(DQ, DVAL)                                                                                        \
     if (head_dim == DQ && v_head_dim == DVAL)                                                                           \
         return se::dec::launch<DQ, DVAL>(q, cache, table, table_stride, seq_rows, token_seq, positions, out, part_o,   \

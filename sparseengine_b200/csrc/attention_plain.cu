@@ -9,7 +9,9 @@
 // the keys [kv head][slot][d] and then the values [kv head][slot][dv].
 // Options: `softcap` c > 0 caps the scaled score, s <- c tanh(s / c); `sink` adds a key of score 0
 // that has no value (one more term, exp(0), in the softmax's denominator); `gate` (with its row
-// pitch) multiplies the output element by element with sigmoid(gate[t][h * dv + i]).  Reference: src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127,
+// pitch) multiplies the output element by element with sigmoid(gate[t][h * dv + i]); `sink_logits`
+// (one per query head) puts a learned logit in the place of the sink's 0, unscaled; `keep_first` n > 0
+// (with a window) keeps keys 0..n-1 visible beside the window's.  Reference: src/sparseengine/kernels/triton/context_flashattention_nopad.py:92-127,
 // src/sparseengine/kernels/triton/gqa_flash_decoding_stage1.py:69-120.
 //
 // A block-table entry outside [0, num_pages) is not followed: the key is left out and a code
@@ -29,7 +31,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
                                              const int* __restrict__ positions, T* __restrict__ out, int hq, int hkv,
                                              int d, int dv, int page_size, float scale, int window, int num_pages,
                                              int* __restrict__ error, float softcap, int sink,
-                                             const T* __restrict__ gate, int gate_pitch) {
+                                             const T* __restrict__ gate, int gate_pitch,
+                                             const float* __restrict__ sink_logits, int keep_first) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = h / (hq / hkv);
@@ -49,7 +52,10 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
         acc[i] = 0.f;
     }
     float m = -INFINITY, l = 0.f;
-    for (int j = lo + warp; j <= pos; j += kAttnWarps) {
+    // the keys in the order they are visited: the kept first ones that lie before the window, then the window's
+    const int kept = min(keep_first, lo), seen = kept + pos - lo + 1;
+    for (int n = warp; n < seen; n += kAttnWarps) {
+        const int j = n < kept ? n : lo + n - kept;
         const int page = row_table[j / page_size];
         if (!page_in_pool(page, num_pages, error, SE_CODE_BAD_PAGE_ATTN_PLAIN)) continue;     // warp-uniform: the key is left out
         const T* kp = cache + (size_t)page * page_elems + head_off + (size_t)(j % page_size) * d;
@@ -84,8 +90,9 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
     float mt = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) mt = fmaxf(mt, sm[w]);
-    if (sink) mt = fmaxf(mt, 0.f);
-    float lt = sink ? expf(-mt) : 0.f;
+    const float sink_logit = sink_logits != nullptr ? sink_logits[h] : 0.f;
+    if (sink) mt = fmaxf(mt, sink_logit);
+    float lt = sink ? expf(sink_logit - mt) : 0.f;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) lt += sm[w] == -INFINITY ? 0.f : sl[w] * expf(sm[w] - mt);
     T* op = out + ((size_t)t * hq + h) * dv;
@@ -105,15 +112,17 @@ extern "C" int se_paged_attention_plain(const void* q, const void* cache, const 
                                         const int* seq_rows, const int* token_seq, const int* positions, void* out,
                                         int tokens, int hq, int hkv, int d, int dv, int page_size, float scale, int window,
                                         int num_pages, int* error, float softcap, int sink, const void* gate, int gate_pitch,
-                                        int dtype, cudaStream_t stream) {
+                                        const float* sink_logits, int keep_first, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (softcap < 0.f || (gate != nullptr && gate_pitch < hq * dv)) return SE_ERR_ARGUMENT;
+    if (softcap < 0.f || (gate != nullptr && gate_pitch < hq * dv) || keep_first < 0) return SE_ERR_ARGUMENT;
+    if (sink_logits != nullptr) sink = 1;
     if (d > 32 * se::kMaxDimPerLane || d <= 0 || dv > 32 * se::kMaxDimPerLane || dv <= 0 || hkv <= 0 || hq % hkv)
         return SE_ERR_UNSUPPORTED;
     dim3 grid(tokens, hq);
     SE_DISPATCH_DTYPE(dtype, T,
         se::paged_attention_plain_kernel<T><<<grid, 32 * se::kAttnWarps, 0, stream>>>(
             (const T*)q, (const T*)cache, table, table_stride, seq_rows, token_seq, positions, (T*)out, hq, hkv, d, dv,
-            page_size, scale, window, num_pages, error, softcap, sink, (const T*)gate, gate_pitch));
+            page_size, scale, window, num_pages, error, softcap, sink, (const T*)gate, gate_pitch,
+            sink_logits, keep_first));
     SE_LAUNCH_CHECK();
 }

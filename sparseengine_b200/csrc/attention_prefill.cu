@@ -76,7 +76,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int k_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
     const int k_begin = (k_lo / kTileKeys) * kTileKeys;
     const int k_end = max_pos + 1;
-    const int num_tiles = (k_end - k_begin + kTileKeys - 1) / kTileKeys;
+    // first keys that stay visible: those before the CTA's window come as tiles of their own, ahead of the window's
+    const int keep_first = window > 0 ? opt.keep_first : 0;
+    const int kept = min(keep_first, k_lo);
+    const int kept_tiles = (kept + kTileKeys - 1) / kTileKeys;
+    const int num_tiles = kept_tiles + (k_end - k_begin + kTileKeys - 1) / kTileKeys;
 
     const int* row_table = table + (size_t)seq_rows[entry] * table_stride;
     const size_t page_elems = (size_t)hkv * page_size * (D + DV);
@@ -107,7 +111,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     // Rows [64][DIM] of a tile: a thread copies chunk (tid % chunks) of rows tid / chunks + k * (kThreads / chunks).
     // The rows' addresses are looked up first (independent loads), so that no table load sits
     // between the asynchronous copies.  `off`: where the head's rows start in a page; DIM elements a row.
-    auto load_rows = [&](auto dim_tag, uint8_t* dst, int base, size_t off) {
+    auto load_rows = [&](auto dim_tag, uint8_t* dst, int base, size_t off, int k_lo, int k_end) {
         constexpr int DIM = decltype(dim_tag)::value;
         constexpr int kChunks = DIM / 8;
         constexpr int kRowStep = kThreads / kChunks, kIters = kTileKeys / kRowStep;
@@ -135,9 +139,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     };
     auto load_tile = [&](int tile, int stage) {
         uint8_t* kbase = smem + (size_t)stage * kStageBytes;
-        const int base = k_begin + tile * kTileKeys;
-        load_rows(std::integral_constant<int, D>{}, kbase, base, head_off);
-        load_rows(std::integral_constant<int, DV>{}, kbase + kTileBytes, base, v_off);
+        const bool first = tile < kept_tiles;
+        const int base = first ? tile * kTileKeys : k_begin + (tile - kept_tiles) * kTileKeys;
+        const int from = first ? 0 : k_lo, to = first ? kept : k_end;       // the keys of this tile that are read
+        load_rows(std::integral_constant<int, D>{}, kbase, base, head_off, from, to);
+        load_rows(std::integral_constant<int, DV>{}, kbase + kTileBytes, base, v_off, from, to);
     };
 
     for (int s = 0; s < kStages - 1; ++s) {
@@ -154,7 +160,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         if (tile + kStages - 1 < num_tiles) load_tile(tile + kStages - 1, (tile + kStages - 1) % kStages);
         cp_async_commit();
 
-        const int key0 = k_begin + tile * kTileKeys;
+        const bool first = tile < kept_tiles;
+        const int key0 = first ? tile * kTileKeys : k_begin + (tile - kept_tiles) * kTileKeys;
         if (key0 > warp_max_pos || row_base + warp * 16 >= total_rows) continue;   // warp-uniform: nothing visible
         const int stage = tile % kStages;
         const uint32_t kaddr = smem_u32(smem + (size_t)stage * kStageBytes);
@@ -182,7 +189,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
             for (int e = 0; e < 4; ++e) {
                 const int j = key0 + n * 8 + 2 * t4 + (e & 1);
                 const int h = e >> 1;
-                if (j > pos[h] || j < lo[h]) s[n][e] = -INFINITY;
+                // a kept tile: its keys lie before every row's window and are seen by all; a window tile: keys up to
+                // the row's position, from its window's start or among the kept first
+                if (first ? j >= kept : (j > pos[h] || (j < lo[h] && j >= keep_first) || j < kept)) s[n][e] = -INFINITY;
                 mx[h] = fmaxf(mx[h], s[n][e]);
             }
         float corr[2], m_use[2];
@@ -239,7 +248,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int h = 0; h < 2; ++h) {
         if (!valid[h]) continue;
         // the sink's term 2^(0 - m): it grows beyond the type only where the keys hold nothing (the output is 0 then)
-        if (opt.sink) l_run[h] += exp2f(-m_run[h] * scale_log2);
+        if (opt.sink) l_run[h] += exp2f(sink_log2(opt, head[h]) - m_run[h] * scale_log2);
         const float inv = 1.f / l_run[h];
         __nv_bfloat16* dst = out + ((size_t)tok[h] * hq + head[h]) * DV;
         const __nv_bfloat16* gp = opt.gate != nullptr ? opt.gate + (size_t)tok[h] * opt.gate_pitch + (size_t)head[h] * DV : nullptr;
@@ -293,13 +302,15 @@ extern "C" int se_attn_prefill(const void* q, const void* cache, const int* tabl
                                const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int entries,
                                int max_q_len, int hq, int hkv, int head_dim, int v_head_dim, int page_size, float scale,
                                int window, int num_pages, int* error, float softcap, int sink, const void* gate,
-                               int gate_pitch, cudaStream_t stream) {
+                               int gate_pitch, const float* sink_logits, int keep_first, cudaStream_t stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!(head_dim == 64 || head_dim == 128) || hkv <= 0 || hq % hkv || entries > 65535 || hkv > 65535)
         return SE_ERR_UNSUPPORTED;
-    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * v_head_dim)) return SE_ERR_ARGUMENT;
-    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink,
-                                      (const __nv_bfloat16*)gate, gate_pitch};
+    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * v_head_dim) || keep_first < 0)
+        return SE_ERR_ARGUMENT;
+    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f,
+                                      sink || sink_logits != nullptr, (const __nv_bfloat16*)gate, gate_pitch, sink_logits,
+                                      window > 0 ? keep_first : 0};
 #define SE_PREFILL_CASE(DQ, DVAL)                                                                                      \
     if (head_dim == DQ && v_head_dim == DVAL)                                                                          \
         return se::pre::launch<DQ, DVAL>(q, cache, table, table_stride, seq_rows, cu_q, kv_len, out, entries, max_q_len, \

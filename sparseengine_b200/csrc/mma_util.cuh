@@ -50,12 +50,20 @@ template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 //   sink            : a key of score 0 without a value joins the softmax's denominator.
 //   gate, gate_pitch: the output is multiplied element by element with sigmoid(gate[t][h * dv + i])
 //                     (rows gate_pitch elements apart); nullptr: no gate.
+//   sink_logits     : with `sink`, a learned logit per query head in the place of the sink's 0 (unscaled); nullptr: 0.
+//   keep_first      : with a window, keys 0 .. keep_first-1 stay visible beside the window's.
 struct SoftmaxOptions {
     float cap_in, cap_out;
     int sink;
     const __nv_bfloat16* gate;
     int gate_pitch;
+    const float* sink_logits;
+    int keep_first;
 };
+// the sink's logit of a head, times log2(e)
+__device__ __forceinline__ float sink_log2(const SoftmaxOptions& opt, int head) {
+    return opt.sink_logits != nullptr ? opt.sink_logits[head] * 1.4426950408889634f : 0.f;
+}
 
 // cap_out * tanh(s * cap_in) with tanh(x) = 1 - 2 / (exp(2x) + 1); beyond |x| = 15 tanh is 1 in 32-bit.
 __device__ __forceinline__ float capped_score(float s, float cap_in, float cap_out) {

@@ -123,7 +123,10 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
     }
     for (int a = blockIdx.x * blockDim.x + threadIdx.x; a < assignments; a += gridDim.x * blockDim.x) {
         const int e = ids[a];
-        if ((unsigned)e >= (unsigned)experts) continue;      // not an expert: no rank was written for it, nothing is indexed with it
+        if ((unsigned)e >= (unsigned)experts) {      // not an expert with weights: it gets no row (the sum over the slots knows what it stands for)
+            inv_pos[a] = -1;
+            continue;
+        }
         const int p = off[e] + rank[a];
         sorted[p] = a;
         inv_pos[a] = p;
@@ -169,7 +172,10 @@ moe_route_small_kernel(const int* __restrict__ ids, int assignments, int experts
     scan_counts(cnt, experts, tile_rows, off, toff);
     for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
         const int e = ids_s[a];
-        if ((unsigned)e >= (unsigned)experts) continue;      // not an expert: the caller's fault, nothing is read out of range
+        if ((unsigned)e >= (unsigned)experts) {      // not an expert with weights: it gets no row
+            if (blockIdx.x == 0) inv_pos[a] = -1;
+            continue;
+        }
         const int p = off[e] + rank_s[a];
         sorted_s[p] = a;
         if (blockIdx.x == 0) {
@@ -286,20 +292,31 @@ __global__ void grouped_gemm_plain_kernel(const T* __restrict__ a, const T* __re
 }
 
 // out[t, :] = cast(sum over slots (32-bit, slot order) of y[inv_pos[t * top_k + slot], :] (+ add[t, :], last)).
+// A slot without a row (inv_pos < 0) stands for an expert whose output is its input: with `x` and `weights`
+// it adds weights[t * top_k + slot] * x[t, :], without them nothing.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv_pos, const T* __restrict__ add,
-                                   T* __restrict__ out, int hidden, int top_k) {
+                                   T* __restrict__ out, int hidden, int top_k, const T* __restrict__ x,
+                                   const float* __restrict__ weights) {
     grid_dependency_trigger();       // the norm that follows may fetch its weights, and the projection after it its own
     const int t = blockIdx.x;
-    if ((hidden & 7) == 0 && aligned8(y) && aligned8(out) && (add == nullptr || aligned8(add))) {
+    if ((hidden & 7) == 0 && aligned8(y) && aligned8(out) && (add == nullptr || aligned8(add)) && (x == nullptr || aligned8(x))) {
         const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
         if (i >= hidden) return;
         float acc[8] = {};
         for (int k = 0; k < top_k; ++k) {
             float v[8];
-            load8(y + (size_t)inv_pos[t * top_k + k] * hidden + i, v);
+            const int p = inv_pos[t * top_k + k];
+            if (p >= 0) {
+                load8(y + (size_t)p * hidden + i, v);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+                for (int j = 0; j < 8; ++j) acc[j] += v[j];
+            } else if (x != nullptr) {
+                const float wk = weights[t * top_k + k];
+                load8(x + (size_t)t * hidden + i, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += wk * v[j];
+            }
         }
         if (add != nullptr) {
             float v[8];
@@ -313,7 +330,11 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
     for (int i = blockIdx.y * blockDim.x * 8 + threadIdx.x; i < min(hidden, (int)(blockIdx.y + 1) * (int)blockDim.x * 8);
          i += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top_k; ++k) s += to_float(y[(size_t)inv_pos[t * top_k + k] * hidden + i]);
+        for (int k = 0; k < top_k; ++k) {
+            const int p = inv_pos[t * top_k + k];
+            if (p >= 0) s += to_float(y[(size_t)p * hidden + i]);
+            else if (x != nullptr) s += weights[t * top_k + k] * to_float(x[(size_t)t * hidden + i]);
+        }
         if (add != nullptr) s += to_float(add[(size_t)t * hidden + i]);
         out[(size_t)t * hidden + i] = from_float<T>(s);
     }
@@ -403,10 +424,12 @@ extern "C" int se_moe_grouped_gemm_plain(int mode, const void* a, const void* w,
 }
 
 extern "C" int se_moe_combine(const void* y, const int* inv_pos, const void* add, void* out, int tokens, int hidden, int top_k,
-                              int dtype, cudaStream_t stream) {
+                              const void* x, const float* weights, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if ((x == nullptr) != (weights == nullptr)) return SE_ERR_ARGUMENT;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 128 * 8)), 128, 0, stream>>>((const T*)y, inv_pos, (const T*)add, (T*)out, hidden, top_k));
+        se::moe_combine_kernel<T><<<dim3(tokens, se::ceil_div(hidden, 128 * 8)), 128, 0, stream>>>(
+            (const T*)y, inv_pos, (const T*)add, (T*)out, hidden, top_k, (const T*)x, weights));
     SE_LAUNCH_CHECK();
 }
 

@@ -49,6 +49,8 @@ LIMITS = {
     "recurrent_max_state_rows": 512,        # rows of a recurrence's state on the key/state side (16 registers x 32 lanes)
     "latent_max_row": 1024,                 # latent plus shared key part of one position (32 registers x 32 lanes)
     "retention_max_head_dim": 256,          # rows of a retention state (32 registers x 8 warps)
+    "stream_mix_max_streams": 8,            # a column's stream values live in registers
+    "memory_max_head_dim": 256,             # rows of a matrix memory's state (32 registers x 8 warps)
     "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
 }
 
@@ -184,45 +186,65 @@ def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cach
     return q_out
 
 
+def _has_sink(sink) -> int:
+    return 1 if isinstance(sink, torch.Tensor) else int(bool(sink))
+
+
+def _sink_logits(sink, num_heads: int):
+    """The pointer of a learned sink's logits (one 32-bit number per query head), or None."""
+    if not isinstance(sink, torch.Tensor):
+        return None
+    if sink.shape != (num_heads,):
+        raise ValueError(f"a learned sink has one logit per query head ({num_heads}), got {tuple(sink.shape)}")
+    return _ptr(sink, torch.float32, "sink")
+
+
 def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads,
                           head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
-                          sink: bool = False, gate=None):
+                          sink=False, gate=None, keep_first: int = 0):
     """``v_head_dim``: the values' head size where it differs from the queries' and keys'.
-    ``softcap`` c: scaled scores become c tanh(s / c).  ``sink``: a key of score 0 without a value
-    joins the softmax's denominator.  ``gate``: a matrix (rows may be a view with a pitch) whose
-    sigmoid multiplies the output, [tokens, num_heads * v_head_dim]."""
+    ``softcap`` c: scaled scores become c tanh(s / c).  ``sink``: True: a key of score 0 without a value
+    joins the softmax's denominator; a 32-bit tensor [num_heads]: its logit is the head's entry (unscaled).
+    ``gate``: a matrix (rows may be a view with a pitch) whose sigmoid multiplies the output,
+    [tokens, num_heads * v_head_dim].  ``keep_first`` n (with a window): keys 0..n-1 stay visible."""
     tokens = q.shape[0]
     dt = q.dtype
     if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1 or gate.dtype != dt):
         raise ValueError("gate must be a matrix of q's dtype with contiguous rows")
-    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiiii" "f" "iip" "fipi" "ip")(
+    sink_logits = _sink_logits(sink, num_heads)
+    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiiii" "f" "iip" "fipi" "pi" "ip")(
         _ptr(q, None, "q"), _ptr(cache, dt, "cache"), _ptr(table, torch.int32, "table"), table.shape[1],
         _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, dt, "out"), tokens, num_heads, num_kv_heads,
         head_dim, int(v_head_dim or head_dim), page_size, float(scale), int(window or 0),
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
-        float(softcap or 0.0), int(bool(sink)), gate.data_ptr() if gate is not None else None,
-        gate.stride(0) if gate is not None else 0, dtype_code(dt), _stream()), "paged_attention_plain")
+        float(softcap or 0.0), _has_sink(sink), gate.data_ptr() if gate is not None else None,
+        gate.stride(0) if gate is not None else 0, sink_logits, int(keep_first or 0), dtype_code(dt), _stream()),
+        "paged_attention_plain")
     return out
 
 
 def qk_prep_general(proj, q_w, k_w, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads, num_kv_heads,
                     head_dim, v_head_dim, eps, page_size, has_kv=True, temperature=None, num_pages=None,
-                    inv_freq=None, rotary_dim: int = 0, v_first=None, v_mix=None):
+                    inv_freq=None, rotary_dim: int = 0, v_first=None, v_mix=None, bias=None, per_head: bool = False):
     """Query/key preparation in 32-bit, rounded once: whole-projection RMS norms (optional), a rotation
     of the first ``rotary_dim`` dims of every head (split halves, angles ``position * inv_freq``), a query
     temperature ``(coef, every)`` (q times 1 + coef ln(floor((p+1)/every) + 1)), keys and values of
     different head sizes into their page; ``has_kv=False``: the row holds queries only.
     ``v_first`` (a matrix with contiguous rows, [tokens, kv heads * v_head_dim]) and ``v_mix`` (one 32-bit
-    number on the device): the values written are ``(1 - v_mix) v + v_mix v_first``."""
+    number on the device): the values written are ``(1 - v_mix) v + v_mix v_first``.
+    ``bias`` (32-bit, one per column of the projection row): added before anything else.  ``per_head``: the
+    norms are per head, with weights of ``head_dim`` elements shared by the heads."""
     tokens = proj.shape[0]
+    if bias is not None and bias.numel() != num_heads * head_dim + (num_kv_heads * (head_dim + int(v_head_dim)) if has_kv else 0):
+        raise ValueError("qk_prep_general: the bias has one entry per column of the projection row")
     dt = proj.dtype
     if proj.dim() != 2 or proj.stride(1) != 1:
         raise ValueError("proj must be a matrix with contiguous rows")
     coef, every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
     if v_first is not None and (v_first.dim() != 2 or v_first.stride(1) != 1 or v_first.dtype != dt or v_mix is None):
         raise ValueError("v_first must be a matrix of proj's dtype with contiguous rows, and comes with v_mix")
-    _check(_fn("se_qk_prep_general", "pipp" "pipip" "ppp" "pi" "pp" "iiiii" "f" "fi" "iiip" "ip")(
+    _check(_fn("se_qk_prep_general", "pipp" "pipip" "ppp" "pi" "pp" "iiiii" "f" "fi" "iiip" "pi" "ip")(
         proj.data_ptr(), proj.stride(0), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
         _ptr(inv_freq, torch.float32, "inv_freq"), int(rotary_dim), v_first.data_ptr() if v_first is not None else None,
         v_first.stride(0) if v_first is not None else 0, _ptr(v_mix, torch.float32, "v_mix") if v_first is not None else None,
@@ -231,7 +253,7 @@ def qk_prep_general(proj, q_w, k_w, positions, token_seq, seq_rows, table, cache
         _ptr(cache, dt, "cache") if has_kv else None, _ptr(q_out, dt, "q_out"), tokens, num_heads, num_kv_heads, head_dim,
         int(v_head_dim), float(eps), coef, every, page_size, int(bool(has_kv)),
         (cache.shape[0] if num_pages is None else int(num_pages)) if has_kv else 0, _ptr(error_word(proj.device)),
-        dtype_code(dt), _stream()), "qk_prep_general")
+        _ptr(bias, torch.float32, "bias"), int(bool(per_head)), dtype_code(dt), _stream()), "qk_prep_general")
     return q_out
 
 
@@ -518,12 +540,16 @@ def gated_group_norm(y, proj, z_off: int, w, out, *, parts: int, eps: float):
 
 
 def delta_prep(qkv, a, proj, b_off: int, dt_bias, a_log, dec, beta, *, heads, kv_heads, head_dim, v_head_dim,
-               unit_eps: float, q_scale: float):
-    _check(_fn("se_delta_prep", "pppii" "pp" "pp" "iiiii" "ff" "ip")(
-        _ptr(qkv, torch.float32, "qkv"), _ptr(a, proj.dtype, "a"), proj.data_ptr(), proj.stride(0), int(b_off),
+               unit_eps: float, q_scale: float, per_head: bool = False):
+    """``a``: the decay projection, ``[tokens, heads * head_dim]`` or (``per_head``) ``[tokens, heads]``; it may
+    be a view of columns of the input projection (rows ``a.stride(0)`` apart)."""
+    if a.dtype != proj.dtype or a.stride(-1) != 1:
+        raise TypeError("delta_prep: the decay projection must have the projection's type and unit column stride")
+    _check(_fn("se_delta_prep", "ppipii" "pp" "pp" "iiiii" "ff" "iip")(
+        _ptr(qkv, torch.float32, "qkv"), a.data_ptr(), a.stride(0), proj.data_ptr(), proj.stride(0), int(b_off),
         _ptr(dt_bias, torch.float32), _ptr(a_log, torch.float32), _ptr(dec, torch.float32), _ptr(beta, torch.float32),
-        qkv.shape[0], heads, kv_heads, head_dim, v_head_dim, float(unit_eps), float(q_scale), dtype_code(proj.dtype),
-        _stream()), "delta_prep")
+        qkv.shape[0], heads, kv_heads, head_dim, v_head_dim, float(unit_eps), float(q_scale), int(per_head),
+        dtype_code(proj.dtype), _stream()), "delta_prep")
 
 
 def delta_scan(qkv, dec, beta, state, step, o, *, heads, kv_heads, head_dim, v_head_dim):
@@ -534,11 +560,99 @@ def delta_scan(qkv, dec, beta, state, step, o, *, heads, kv_heads, head_dim, v_h
     return o
 
 
-def delta_out(o, gate, w, out, *, v_head_dim: int, eps: float):
+def delta_out(o, gate, w, out, *, heads: int, v_head_dim: int, eps: float, silu: bool = False):
+    """``gate`` [tokens, heads * v_head_dim] may be a view of columns of a projection; ``silu``: the gate is
+    ``g * sigmoid(g)`` instead of ``sigmoid(g)``."""
     rows = o.numel() // v_head_dim
-    _check(_fn("se_delta_out", "pppp" "ii" "f" "ip")(
-        _ptr(o, torch.float32, "o"), _ptr(gate, out.dtype, "gate"), _ptr(w, torch.float32, "w"), _ptr(out), rows,
-        v_head_dim, float(eps), dtype_code(out.dtype), _stream()), "delta_out")
+    if gate.dtype != out.dtype or gate.stride(-1) != 1:
+        raise TypeError("delta_out: the gate must have the output's type and unit column stride")
+    _check(_fn("se_delta_out", "ppipp" "iii" "f" "iip")(
+        _ptr(o, torch.float32, "o"), gate.data_ptr(), gate.stride(0), _ptr(w, torch.float32, "w"), _ptr(out), rows,
+        heads, v_head_dim, float(eps), int(silu), dtype_code(out.dtype), _stream()), "delta_out")
+    return out
+
+
+# ---- matrix memory (csrc/matrix_memory.cu) ---------------------------------------------------
+
+def memory_gates(proj, i_off: int, f_off: int, bias, cap: float, state, m_off: int, step, gates, *, heads: int):
+    """The gates of a matrix memory: ``gates[t, h] = (keep, take, exp(-m))`` from the log input and forget
+    gates (columns ``i_off + h`` and ``f_off + h`` of the projection, plus ``bias`` [2, heads]), each
+    ``cap tanh(. / cap)``; the running maximum ``m`` lives at ``state[row, m_off + h]`` and is brought up to date."""
+    _check(_fn("se_memory_gates", "piii" "pf" "pli" "pp" "p" "ii" "ip")(
+        proj.data_ptr(), proj.stride(0), int(i_off), int(f_off), _ptr(bias, torch.float32, "bias"), float(cap),
+        _ptr(state, torch.float32, "state"), state.stride(0), int(m_off), _ptr(step.cu_q), _ptr(step.seq_rows),
+        _ptr(gates, torch.float32, "gates"), step.num_seqs, heads, dtype_code(proj.dtype), _stream()), "memory_gates")
+    return gates
+
+
+def memory_scan(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float, state, step, o, *, heads, head_dim,
+                v_head_dim):
+    """``S <- keep S + take k [v | 1]^T``, ``o = S^T (q_scale q)`` token by token; ``state[row]`` starts with
+    ``[heads, head_dim, v_head_dim + 1]``; ``o`` [tokens, heads, v_head_dim + 1] (the last column is n . q)."""
+    _check(_fn("se_memory_scan", "piiii" "pf" "pl" "pp" "p" "iiii" "ip")(
+        proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(gates, torch.float32, "gates"),
+        float(q_scale), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
+        _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim, dtype_code(proj.dtype), _stream()),
+        "memory_scan")
+    return o
+
+
+def memory_out(o, gates, proj, g_off: int, w, out, *, heads, v_head_dim, eps: float, den_eps: float,
+               out_scale: float = 1.0):
+    """The read-out of a matrix memory: ``o / (max(|n . q|, exp(-m)) + den_eps)``, each head over its root mean
+    square, times ``w`` [heads * v_head_dim], times sigmoid of the gate's projection (columns from ``g_off``)."""
+    tokens = out.shape[0]
+    _check(_fn("se_memory_out", "pppiip" "pi" "iii" "fff" "ip")(
+        _ptr(o, torch.float32, "o"), _ptr(gates, torch.float32, "gates"), proj.data_ptr(), proj.stride(0), int(g_off),
+        _ptr(w, torch.float32, "w"), out.data_ptr(), out.stride(0), tokens, heads, v_head_dim, float(eps),
+        float(den_eps), float(out_scale), dtype_code(out.dtype), _stream()), "memory_out")
+    return out
+
+
+# ---- several residual streams (csrc/stream_mix.cu) -----------------------------------------------
+
+def stream_embed(table, ids, streams, scale: float = 1.0):
+    """streams[t, s] = table[ids[t]] * scale for every stream s (32-bit)."""
+    tokens, S, width = streams.shape
+    _check(_fn("se_stream_embed", "ppp" "iiii" "f" "ip")(
+        _ptr(table, None, "table"), _ptr(ids, torch.int32, "ids"), _ptr(streams, torch.float32, "streams"), tokens, S,
+        width, table.shape[0], float(scale), dtype_code(table.dtype), _stream()), "stream_embed")
+    return streams
+
+
+def stream_mix(streams, *, write=None, read=None, dtype, store: bool = True):
+    """One kernel over ``streams`` [tokens, S, width] (32-bit, in place).  ``write = (y, gate, gate_bias, mix,
+    out_w)``: ``x_t <- sum_s mix[s, t] x_s + out_w[t] * y'`` with ``y' = y * sigmoid(gate + gate_bias)`` (gate and
+    bias optional).  ``read = (in_w, norm_w, eps, h)``: ``h = norm(sum_s in_w[s] x_s) * norm_w`` (``in_w`` None:
+    ones), read after the write.  ``store=False``: the streams are left as they were."""
+    tokens, S, width = streams.shape
+    y = gate = gate_bias = mix = out_w = in_w = norm_w = h = None
+    eps = 0.0
+    if write is not None:
+        y, gate, gate_bias, mix, out_w = write
+    if read is not None:
+        in_w, norm_w, eps, h = read
+    _check(_fn("se_stream_mix", "piii" "pp" "pppp" "pf" "pi" "ip")(
+        _ptr(streams, torch.float32, "streams"), tokens, S, width, _ptr(y, dtype, "y"), _ptr(gate, dtype, "gate"),
+        _ptr(gate_bias, torch.float32, "gate_bias"), _ptr(mix, torch.float32, "mix"), _ptr(out_w, torch.float32, "out_w"),
+        _ptr(in_w, torch.float32, "in_w"), _ptr(norm_w, torch.float32, "norm_w"), float(eps), _ptr(h, dtype, "h"),
+        int(bool(store)), dtype_code(dtype), _stream()), "stream_mix")
+    return h
+
+
+def stream_sum(streams, out):
+    tokens, S, width = streams.shape
+    _check(_fn("se_stream_sum", "pp" "iii" "p")(
+        _ptr(streams, torch.float32, "streams"), _ptr(out, torch.float32, "out"), tokens, S, width, _stream()), "stream_sum")
+    return out
+
+
+def scaled_sum(x, y, a: float, b: float, out, bias=None):
+    """out = a * x + b * y (+ bias [width], 32-bit), 32-bit arithmetic, rounded once."""
+    rows, width = out.shape
+    _check(_fn("se_scaled_sum", "pp" "ff" "pp" "ii" "ip")(
+        _ptr(x, out.dtype, "x"), _ptr(y, out.dtype, "y"), float(a), float(b), _ptr(bias, torch.float32, "bias"), _ptr(out),
+        rows, width, dtype_code(out.dtype), _stream()), "scaled_sum")
     return out
 
 
@@ -652,13 +766,16 @@ def moe_grouped_gemm_plain(mode: int, a, w, ws: dict, route_w, out, *, max_tiles
     return out
 
 
-def moe_combine(y, inv_pos, out, top_k: int, add=None):
+def moe_combine(y, inv_pos, out, top_k: int, add=None, identity=None):
     """out[t] = the sum over the slots (32-bit, slot order) and, last, of ``add[t]`` ([tokens, hidden], optional:
-    a shared expert's output), rounded once."""
+    a shared expert's output), rounded once.  ``identity = (x, weights)``: a slot that got no row in the routing
+    build (its expert has no weights) adds ``weights[t, slot] * x[t]``."""
     tokens, hidden = out.shape
-    _check(_fn("se_moe_combine", "ppppiiiip")(
+    x, weights = identity if identity is not None else (None, None)
+    _check(_fn("se_moe_combine", "ppppiiippip")(
         _ptr(y, out.dtype, "y"), _ptr(inv_pos, torch.int32, "inv_pos"), _ptr(add, out.dtype, "add"), _ptr(out), tokens,
-        hidden, top_k, dtype_code(out.dtype), _stream()), "moe_combine")
+        hidden, top_k, _ptr(x, out.dtype, "x"), _ptr(weights, torch.float32, "weights"), dtype_code(out.dtype), _stream()),
+        "moe_combine")
     return out
 
 
@@ -853,13 +970,19 @@ def attn_decode_plan(tokens: int, num_heads: int, num_kv_heads: int, max_keys: i
     return splits, per_tiles * 64
 
 
-def _softmax_options(q, gate, num_heads, v_head_dim, softcap, sink):
-    """The tail of the tensor-core attention kernels' arguments: cap, sink, gate pointer, gate pitch."""
+def _softmax_options(q, gate, num_heads, v_head_dim, softcap, sink, keep_first=None):
+    """The tail of the tensor-core attention kernels' arguments: cap, sink, gate pointer, gate pitch and, where
+    ``keep_first`` is given (a number), the learned sink's logits and the count of first keys that stay visible."""
     if gate is not None and (gate.dim() != 2 or gate.stride(1) != 1 or gate.dtype != q.dtype
                              or gate.shape[1] != num_heads * v_head_dim):
         raise ValueError("gate must be a matrix [tokens, heads * value size] of q's dtype with contiguous rows")
-    return (float(softcap or 0.0), int(bool(sink)), gate.data_ptr() if gate is not None else None,
+    tail = (float(softcap or 0.0), _has_sink(sink), gate.data_ptr() if gate is not None else None,
             gate.stride(0) if gate is not None else 0)
+    if keep_first is None:
+        if isinstance(sink, torch.Tensor):
+            raise ValueError("this kernel takes no learned sink")
+        return tail
+    return tail + (_sink_logits(sink, num_heads), int(keep_first))
 
 
 def attn_decode_value_dim_supported(v_head_dim: int) -> bool:
@@ -869,7 +992,7 @@ def attn_decode_value_dim_supported(v_head_dim: int) -> bool:
 
 def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads, head_dim, page_size,
                 scale, window=None, max_keys: int, num_pages=None, step_inputs_settled: bool = False, v_head_dim=None,
-                softcap=None, sink: bool = False, gate=None):
+                softcap=None, sink=False, gate=None, keep_first: int = 0):
     """``step_inputs_settled``: ``table``, ``seq_rows``, ``token_seq`` and ``positions`` were complete
     before the kernel launched just before this call began (that kernel wrote ``q`` and the step's
     keys).  The attention kernel, launched as its dependent, then finds its place in the block table
@@ -882,28 +1005,28 @@ def attn_decode(q, cache, table, seq_rows, token_seq, positions, out, *, num_hea
     if splits > 1:
         part_o = torch.empty(tokens * num_heads * splits * dv, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(tokens * num_heads * splits * 2, dtype=torch.float32, device=q.device)
-    _check(_fn("se_attn_decode", "pppipppppp" "iiiiii" "f" "iii" "ip" "i" "fipi" "p")(
+    _check(_fn("se_attn_decode", "pppipppppp" "iiiiii" "f" "iii" "ip" "i" "fipi" "pi" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, torch.bfloat16, "out"), _ptr(part_o), _ptr(part_ml),
         tokens, num_heads, num_kv_heads, head_dim, dv, page_size, float(scale), int(window or 0), splits, per,
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
-        int(bool(step_inputs_settled)), *_softmax_options(q, gate, num_heads, dv, softcap, sink), _stream()),
-        "attn_decode")
+        int(bool(step_inputs_settled)), *_softmax_options(q, gate, num_heads, dv, softcap, sink, keep_first or 0),
+        _stream()), "attn_decode")
     return out
 
 
 def attn_prefill(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
                  head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
-                 sink: bool = False, gate=None):
+                 sink=False, gate=None, keep_first: int = 0):
     dv = int(v_head_dim or head_dim)
-    _check(_fn("se_attn_prefill", "pppipppp" "iiiiiii" "f" "i" "ip" "fipi" "p")(
+    _check(_fn("se_attn_prefill", "pppipppp" "iiiiiii" "f" "i" "ip" "fipi" "pi" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), entries, max_q_len, num_heads,
         num_kv_heads, head_dim, dv, page_size, float(scale), int(window or 0),
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
-        *_softmax_options(q, gate, num_heads, dv, softcap, sink), _stream()), "attn_prefill")
+        *_softmax_options(q, gate, num_heads, dv, softcap, sink, keep_first or 0), _stream()), "attn_prefill")
     return out
 
 
@@ -914,8 +1037,10 @@ def attn_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int) 
 
 def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,
                     head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
-                    sink: bool = False, gate=None):
+                    sink: bool = False, gate=None, keep_first: int = 0):
     """Prompt-portion attention on tcgen05 (head size 128, values of the same size)."""
+    if keep_first:
+        raise ValueError("the tcgen05 prompt kernel keeps no first keys beside a window")
     if int(v_head_dim or head_dim) != head_dim:
         raise ValueError("the tcgen05 prompt kernel takes values of the keys' head size")
     _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ii" "fipi" "p")(

@@ -623,12 +623,14 @@ static inline void tile_plan(int rows, int columns, int units, int* nsplit, int*
 // ---- prologue of the delta rule ----------------------------------------------------------------
 // One block per token: q and k heads (in qkv, in place) become unit vectors, x / sqrt(sum x^2 +
 // unit_eps), q also times q_scale; dec = exp(-exp(A_log[h]) * softplus(a + dt_bias)); beta =
-// sigmoid(b).  `a` [T, H*d] is the decay projection, `proj` column b_off + h the beta projection.
+// sigmoid(b).  `a` (rows a_pitch apart) is the decay projection: [H*d], one decay per head and key
+// channel, or, with `per_head`, [H], one decay per head (dt_bias likewise), which is written to all
+// of the head's channels.  `proj` column b_off + h is the beta projection.
 template <typename T>
-__global__ void delta_prep_kernel(float* qkv, int width, const T* a, const T* proj, int pitch, int b_off,
+__global__ void delta_prep_kernel(float* qkv, int width, const T* a, int a_pitch, const T* proj, int pitch, int b_off,
                                   const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                   float* __restrict__ dec, float* __restrict__ beta, int H, int G, int d,
-                                  float unit_eps, float q_scale) {
+                                  float unit_eps, float q_scale, int per_head) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     float* row = qkv + (size_t)t * width;
     for (int hh = warp; hh < 2 * G; hh += warps) {          // q heads, then k heads
@@ -640,8 +642,9 @@ __global__ void delta_prep_kernel(float* qkv, int width, const T* a, const T* pr
         for (int i = lane; i < d; i += 32) v[i] *= f;
     }
     for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
-        const float rate = expf(a_log[i / d]);
-        dec[(size_t)t * H * d + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * H * d + i]) + dt_bias[i]));
+        const int h = i / d, j = per_head ? h : i;
+        const float rate = expf(a_log[h]);
+        dec[(size_t)t * H * d + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * a_pitch + j]) + dt_bias[j]));
     }
     for (int h = threadIdx.x; h < H; h += blockDim.x)
         beta[(size_t)t * H + h] = sigmoid_f(to_float(proj[(size_t)t * pitch + b_off + h]));
@@ -649,18 +652,22 @@ __global__ void delta_prep_kernel(float* qkv, int width, const T* a, const T* pr
 
 // ---- epilogues ---------------------------------------------------------------------------------
 // Delta rule: each head's output divided by its root mean square over dv, times w[dv] (shared by
-// the heads), times sigmoid(gate).  One warp per (token, head).
+// the heads), times sigmoid(gate) or (`silu`) gate * sigmoid(gate); the gate's rows lie gate_pitch
+// apart, a head's dv columns side by side.  One warp per (token, head).
 template <typename T>
-__global__ void delta_out_kernel(const float* __restrict__ o, const T* gate, const float* __restrict__ w,
-                                 T* __restrict__ out, int rows, int dv, float eps) {
+__global__ void delta_out_kernel(const float* __restrict__ o, const T* gate, int gate_pitch, const float* __restrict__ w,
+                                 T* __restrict__ out, int rows, int H, int dv, float eps, int silu) {
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= rows) return;
     const float* v = o + (size_t)r * dv;
+    const T* gp = gate + (size_t)(r / H) * gate_pitch + (size_t)(r % H) * dv;
     float ss = 0.f;
     for (int i = lane; i < dv; i += 32) ss += v[i] * v[i];
     const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
-    for (int i = lane; i < dv; i += 32)
-        out[(size_t)r * dv + i] = from_float<T>(v[i] * inv * w[i] * sigmoid_f(to_float(gate[(size_t)r * dv + i])));
+    for (int i = lane; i < dv; i += 32) {
+        const float g = to_float(gp[i]);
+        out[(size_t)r * dv + i] = from_float<T>(v[i] * inv * w[i] * (silu ? g * sigmoid_f(g) : sigmoid_f(g)));
+    }
 }
 
 // State space: y * silu(z), then an RMS norm over each of `parts` equal parts of the row, times
@@ -779,14 +786,15 @@ extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt
     SE_LAUNCH_CHECK();
 }
 
-extern "C" int se_delta_prep(float* qkv, const void* a, const void* proj, int pitch, int b_off, const float* dt_bias,
-                             const float* a_log, float* dec, float* beta, int tokens, int H, int G, int d, int dv,
-                             float unit_eps, float q_scale, int dtype, cudaStream_t stream) {
+extern "C" int se_delta_prep(float* qkv, const void* a, int a_pitch, const void* proj, int pitch, int b_off,
+                             const float* dt_bias, const float* a_log, float* dec, float* beta, int tokens, int H, int G,
+                             int d, int dv, float unit_eps, float q_scale, int per_head, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0) return SE_ERR_ARGUMENT;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || a_pitch < (per_head ? H : H * d)) return SE_ERR_ARGUMENT;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::delta_prep_kernel<T><<<tokens, 256, 0, stream>>>(qkv, 2 * G * d + H * dv, (const T*)a, (const T*)proj, pitch, b_off,
-                                                            dt_bias, a_log, dec, beta, H, G, d, unit_eps, q_scale));
+        se::delta_prep_kernel<T><<<tokens, 256, 0, stream>>>(qkv, 2 * G * d + H * dv, (const T*)a, a_pitch, (const T*)proj, pitch,
+                                                            b_off, dt_bias, a_log, dec, beta, H, G, d, unit_eps, q_scale,
+                                                            per_head));
     SE_LAUNCH_CHECK();
 }
 
@@ -823,11 +831,13 @@ extern "C" int se_delta_scan(const float* qkv, const float* dec, const float* be
     SE_LAUNCH_CHECK();
 }
 
-extern "C" int se_delta_out(const float* o, const void* gate, const float* w, void* out, int rows, int dv, float eps,
-                            int dtype, cudaStream_t stream) {
+extern "C" int se_delta_out(const float* o, const void* gate, int gate_pitch, const float* w, void* out, int rows, int H,
+                            int dv, float eps, int silu, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (H <= 0 || rows % H || gate_pitch < H * dv) return SE_ERR_ARGUMENT;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::delta_out_kernel<T><<<se::ceil_div(rows, 4), 128, 0, stream>>>(o, (const T*)gate, w, (T*)out, rows, dv, eps));
+        se::delta_out_kernel<T><<<se::ceil_div(rows, 4), 128, 0, stream>>>(o, (const T*)gate, gate_pitch, w, (T*)out, rows, H, dv,
+                                                                           eps, silu));
     SE_LAUNCH_CHECK();
 }
 

@@ -1,0 +1,170 @@
+// Several residual streams per token (hyper-connections), 32-bit.
+//
+// A token carries S copies x_1 .. x_S of the residual stream, laid out [token][stream][width].
+// A sublayer reads one mixture of them and writes its result back into all of them:
+//
+//     read :  u   = sum_s a[s] x_s ;  h = u / sqrt(mean(u^2) + eps) * w        (w: the norm's 32-bit weight)
+//     write:  x_t <- sum_s M[s][t] x_s + b[t] * y'                              (all t from the old x)
+//     y' = y * sigmoid(g + c)  where a gate is given (g: the gate's projection, c its bias), else y
+//
+// One kernel does the write of the sublayer that has just run and the read for the next one, one
+// block per token: the S stream values of a column are in registers between the two, the mixture u
+// of the row waits in shared memory for the row's mean square.  Either half may be left out (the
+// first read of a step has nothing to write, the last write of a step reads with a = 1 for the
+// model's last norm).  S = 1 with M = a = b = 1 is the plain pre-norm residual.  Everything is
+// 32-bit; y, g and h have the activation type.
+#include "common.cuh"
+
+namespace se {
+
+constexpr int kMaxStreams = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+stream_mix_kernel(float* streams, int S, int width, const T* __restrict__ y, const T* __restrict__ gate,
+                  const float* __restrict__ gate_bias, const float* __restrict__ mix, const float* __restrict__ out_w,
+                  const float* __restrict__ in_w, const float* __restrict__ norm_w, float eps, T* __restrict__ h,
+                  int store) {
+    extern __shared__ __align__(16) float urow[];
+    __shared__ float scratch[33];
+    __shared__ float sm_mix[kMaxStreams * kMaxStreams], sm_out[kMaxStreams], sm_in[kMaxStreams];
+    const size_t t = blockIdx.x;
+    if (threadIdx.x < S * S && y != nullptr) sm_mix[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) {
+        if (y != nullptr) sm_out[threadIdx.x] = out_w[threadIdx.x];
+        if (h != nullptr) sm_in[threadIdx.x] = in_w != nullptr ? in_w[threadIdx.x] : 1.f;
+    }
+    __syncthreads();
+    float* base = streams + t * S * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x[kMaxStreams];
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s) x[s] = s < S ? base[(size_t)s * width + i] : 0.f;
+        if (y != nullptr) {
+            float yv = to_float(y[t * width + i]);
+            if (gate != nullptr) {
+                const float z = to_float(gate[t * width + i]) + (gate_bias != nullptr ? gate_bias[i] : 0.f);
+                yv *= 1.f / (1.f + expf(-z));
+            }
+            float nx[kMaxStreams];
+#pragma unroll
+            for (int d = 0; d < kMaxStreams; ++d) {
+                float v = 0.f;
+                if (d < S) {
+#pragma unroll
+                    for (int s = 0; s < kMaxStreams; ++s)
+                        if (s < S) v += sm_mix[s * S + d] * x[s];
+                    v += sm_out[d] * yv;
+                }
+                nx[d] = v;
+            }
+#pragma unroll
+            for (int d = 0; d < kMaxStreams; ++d) {
+                x[d] = nx[d];
+                if (d < S && store) base[(size_t)d * width + i] = nx[d];
+            }
+        }
+        if (h != nullptr) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < kMaxStreams; ++s)
+                if (s < S) u += sm_in[s] * x[s];
+            urow[i] = u;
+            ss += u * u;
+        }
+    }
+    if (h == nullptr) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    // every thread reads back the elements it wrote itself
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        h[t * width + i] = from_float<T>(urow[i] * inv * norm_w[i]);
+}
+
+// streams[t][s] = table[ids[t]] * scale for every s (32-bit product)
+template <typename T>
+__global__ void stream_embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ streams,
+                                    int S, int width, int vocab, float scale) {
+    const size_t t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const T* src = table + (size_t)(ok ? id : 0) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = ok ? to_float(src[i]) * scale : 0.f;
+        for (int s = 0; s < S; ++s) streams[(t * S + s) * width + i] = v;
+    }
+}
+
+// out[t] = sum_s streams[t][s] (a debugging aid: the stream as one)
+__global__ void stream_sum_kernel(const float* __restrict__ streams, float* __restrict__ out, int S, int width) {
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < S; ++s) v += streams[(t * S + s) * width + i];
+        out[t * width + i] = v;
+    }
+}
+
+// out = a * x + b * y (+ bias), 32-bit, rounded once: the outputs of mixers that run side by side
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ x, const T* __restrict__ y, float a, float b,
+                                  const float* __restrict__ bias, T* __restrict__ out, size_t n, int width) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = a * to_float(x[i]) + b * to_float(y[i]);
+        if (bias != nullptr) v += bias[i % width];
+        out[i] = from_float<T>(v);
+    }
+}
+
+}  // namespace se
+
+extern "C" int se_scaled_sum(const void* x, const void* y, float a, float b, const float* bias, void* out, int rows,
+                             int width, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t n = (size_t)rows * width;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::scaled_sum_kernel<T><<<blocks, 256, 0, stream>>>((const T*)x, (const T*)y, a, b, bias, (T*)out, n, width));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_stream_mix_max_streams() { return se::kMaxStreams; }
+extern "C" int se_stream_mix_max_width() { return 51200; }
+
+// y == nullptr: no write; h == nullptr: no read.  store = 0: the new streams are not written back
+// (rows gathered for the last norm).
+extern "C" int se_stream_mix(float* streams, int tokens, int S, int width, const void* y, const void* gate,
+                             const float* gate_bias, const float* mix, const float* out_w, const float* in_w,
+                             const float* norm_w, float eps, void* h, int store, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (S <= 0 || S > se::kMaxStreams || width <= 0 || width > se_stream_mix_max_width()) return SE_ERR_UNSUPPORTED;
+    if (y != nullptr && (mix == nullptr || out_w == nullptr)) return SE_ERR_ARGUMENT;
+    if (h != nullptr && norm_w == nullptr) return SE_ERR_ARGUMENT;
+    if (y == nullptr && h == nullptr) return 0;
+    const size_t smem = h != nullptr ? (size_t)width * sizeof(float) : 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(se::stream_mix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        se::stream_mix_kernel<T><<<tokens, threads, smem, stream>>>(streams, S, width, (const T*)y, (const T*)gate, gate_bias, mix,
+                                                                    out_w, in_w, norm_w, eps, (T*)h, store);
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_stream_embed(const void* table, const int* ids, float* streams, int tokens, int S, int width, int vocab,
+                               float scale, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (S <= 0 || width <= 0) return SE_ERR_ARGUMENT;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::stream_embed_kernel<T><<<tokens, 256, 0, stream>>>((const T*)table, ids, streams, S, width, vocab, scale));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_stream_sum(const float* streams, float* out, int tokens, int S, int width, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    se::stream_sum_kernel<<<tokens, 256, 0, stream>>>(streams, out, S, width);
+    SE_LAUNCH_CHECK();
+}

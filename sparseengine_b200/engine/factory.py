@@ -108,5 +108,6 @@ def apply_kernel_tuning(model: Model, tuning: dict) -> None:
             continue
         for b in model.blocks:
             for part in b.parts().values():
-                if hasattr(part, attr):
-                    setattr(part, attr, int(value))
+                for p in (part, *getattr(part, "branches", ())):        # a mixer of mixers: its branches too
+                    if hasattr(p, attr):
+                        setattr(p, attr, int(value))

@@ -16,7 +16,8 @@ import torch
 from ..config.specs import ModelSpec, ParamSpec, Source
 from ..csrc import ops
 from ..parts.base import KVRequest, StateRequest, StepContext, make_norm
-from ..parts.block import PostNormBlock, PreNormBlock, PreNormStreamBlock, SublayerNormBlock, make_block
+from ..parts.block import (PostNormBlock, PreNormBlock, PreNormStreamBlock, StreamMixBlock, SublayerNormBlock,
+                           make_block)
 from ..parts.linear import linear, linear32
 from ..parts.norm import RMSNorm
 
@@ -69,6 +70,14 @@ class Model:
                                         and hasattr(self.final_norm, "forward_stream")):
             raise ValueError("pre_norm_stream blocks need residual_stream='float32', a final norm with forward_stream, "
                              "and no other arrangement beside them")
+        # blocks over several 32-bit streams that carry (result not yet written, streams)
+        self.multi_stream = any(isinstance(b, StreamMixBlock) for b in self.blocks)
+        if self.multi_stream and not (all(isinstance(b, StreamMixBlock) for b in self.blocks)
+                                      and spec.residual_stream == "float32" and isinstance(self.final_norm, RMSNorm)
+                                      and spec.streams >= 1
+                                      and all(b.mixer_streams.spec.streams == spec.streams for b in self.blocks)):
+            raise ValueError("stream_mix blocks need residual_stream='float32', ModelSpec.streams equal to every block's, "
+                             "an RMS final norm with a 32-bit weight, and no other arrangement beside them")
         self.reinject = None
         if any(e.reinject for e in spec.order) and not (self.pending_stream and spec.reinject_source):
             raise ValueError("ScheduleEntry.reinject needs pre_norm_stream blocks and ModelSpec.reinject_source")
@@ -166,6 +175,8 @@ class Model:
             e1.record()
             self.profile.setdefault(name, []).append((e0, e1))
             return out
+        if isinstance(block, StreamMixBlock):
+            return block.forward(hidden, residual, step, slot, timed=timed)
         if isinstance(block, PostNormBlock):
             y = timed("mixer." + block.mixer.spec.kind, block.mixer.forward, hidden, step, slot)
             hidden, residual = timed("mixer_norm", block.mixer_norm.forward_stream, residual, y, block.alpha)
@@ -204,7 +215,12 @@ class Model:
         hidden = torch.empty(step.num_tokens, s.hidden_size, dtype=self.dtype, device=step.token_ids.device)
         pending_stream = self.pending_stream
         x0 = x0_term = None
-        if pending_stream:
+        if self.multi_stream:
+            # (result not yet written, streams [tokens, S, width]): every stream starts as the scaled embedding
+            residual = torch.empty(step.num_tokens, s.streams, s.hidden_size, dtype=torch.float32, device=hidden.device)
+            ops.stream_embed(self.embed, step.token_ids, residual, scale=s.embed_scale)
+            hidden = None
+        elif pending_stream:
             # (output not yet added, 32-bit stream); `hidden` keeps the embedding output for the re-injections
             residual = torch.empty(hidden.shape, dtype=torch.float32, device=hidden.device)
             ops.embed_stream(self.embed, step.token_ids, residual, hidden if self.dtype != torch.float32 else None,
@@ -237,7 +253,12 @@ class Model:
                 hidden, residual = block.forward(hidden, residual, step, slot)
             else:
                 hidden, residual = self._timed_block(block, hidden, residual, step, slot)
-            if self.stream_taps is not None:
+            if self.stream_taps is not None and self.multi_stream:
+                both = residual.clone()          # the streams with the result they have not taken in yet, as one
+                ops.stream_mix(both, write=hidden[0].write_args(hidden[1], hidden[2]), dtype=self.dtype)
+                self.stream_taps.append(ops.stream_sum(both, torch.empty(both.shape[0], both.shape[2], dtype=torch.float32,
+                                                                         device=both.device)))
+            elif self.stream_taps is not None:
                 tap = (residual if stream32 else hidden).float().clone()
                 if pending_stream and hidden is not None:
                     tap += hidden.float()
@@ -245,7 +266,21 @@ class Model:
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()
-        if pending_stream:  # the wanted rows of the stream and of what it has not taken in yet
+        if self.multi_stream:
+            # the wanted rows of the streams and of what they have not taken in yet; the last norm reads their sum
+            r = torch.empty(n, s.streams * s.hidden_size, dtype=torch.float32, device=residual.device)
+            ops.gather_rows(residual.view(step.num_tokens, -1), want_rows, r)
+            mix, y, gate = hidden
+            yr = torch.empty(n, s.hidden_size, dtype=self.dtype, device=r.device)
+            ops.gather_rows(y, want_rows, yr)
+            gr = None
+            if gate is not None:
+                gr = torch.empty(n, s.hidden_size, dtype=self.dtype, device=r.device)
+                ops.gather_rows(gate, want_rows, gr)
+            h = torch.empty(n, s.hidden_size, dtype=self.dtype, device=r.device)
+            ops.stream_mix(r.view(n, s.streams, s.hidden_size), write=mix.write_args(yr, gr),
+                           read=(None, self.final_norm.weight, self.final_norm.spec.eps, h), dtype=self.dtype, store=False)
+        elif pending_stream:  # the wanted rows of the stream and of what it has not taken in yet
             r = torch.empty(n, s.hidden_size, dtype=torch.float32, device=residual.device)
             ops.gather_rows(residual, want_rows, r)
             p = None

@@ -1,2 +1,2 @@
 """Architecture builders.  Importing this package registers them."""
-from . import bavutar, kisusun, minimax_m2, zisevik  # noqa: F401
+from . import bavutar, kisusun, minimax_m2, tedisun, zisevik  # noqa: F401

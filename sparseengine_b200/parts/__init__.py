@@ -1,3 +1,3 @@
 """Parts a model is assembled from: norms, position encodings, mixers, feed-forwards."""
-from . import attention, latent_attention, mlp, moe, norm, position, recurrent  # noqa: F401  (register the built-in kinds)
+from . import attention, latent_attention, mlp, moe, norm, parallel, position, recurrent, streams  # noqa: F401  (register the built-in kinds)
 from .base import *  # noqa: F401,F403

@@ -47,23 +47,28 @@ class PagedAttention(Mixer):
             if s.q_temperature is not None and not (len(s.q_temperature) == 2 and int(s.q_temperature[1]) > 0):
                 raise ValueError("q_temperature is (coef, every) with every > 0")
         elif (s.v_head_dim not in (None, s.head_dim) or s.q_temperature is not None or not s.own_kv
-              or s.score_softcap is not None or s.sink is not None or s.output_gate or s.value_mix is not None):
-            raise ValueError("v_head_dim, q_temperature, own_kv=False, score_softcap, sink, output_gate and value_mix "
-                             "need prep='general'")
+              or s.score_softcap is not None or s.sink is not None or s.output_gate or s.value_mix is not None
+              or s.bias or s.keep_first or s.qk_norm == "per_head"):
+            raise ValueError("v_head_dim, q_temperature, own_kv=False, score_softcap, sink, output_gate, value_mix, "
+                             "bias, keep_first and per-head norms need prep='general'")
         elif s.head_dim <= 0 or s.head_dim % 16 or s.head_dim > ops.LIMITS["attention_max_head_dim"]:
             raise ValueError(f"head_dim {s.head_dim} is not supported (multiples of 16 up to "
                              f"{ops.LIMITS['attention_max_head_dim']})")
         if s.num_heads > ops.LIMITS["grid_dim_yz"]:
             raise ValueError(f"{s.num_heads} query heads are not supported (at most {ops.LIMITS['grid_dim_yz']}: "
                              "heads are a grid dimension of the attention kernels)")
-        if s.qk_norm not in (None, "whole_projection"):
-            raise ValueError(f"qk_norm {s.qk_norm!r} is not supported")
+        if s.qk_norm not in (None, "whole_projection", "per_head"):
+            raise ValueError(f"qk_norm {s.qk_norm!r} is not supported (None, 'whole_projection' or 'per_head')")
+        if s.keep_first < 0 or (s.keep_first and s.window is None):
+            raise ValueError("keep_first is a count of first positions that stay visible beside a window")
+        if s.bias and (s.output_gate or not s.own_kv):
+            raise ValueError("biases go with projections of q, k and v alone")
         if s.window is not None and s.window <= 0:
             raise ValueError("window must be positive (None: all keys)")
         if s.score_softcap is not None and not s.score_softcap > 0:
             raise ValueError("score_softcap must be positive (None: no cap)")
-        if s.sink not in (None, "zero"):
-            raise ValueError(f"sink {s.sink!r} is not known (None or 'zero')")
+        if s.sink not in (None, "zero", "learned"):
+            raise ValueError(f"sink {s.sink!r} is not known (None, 'zero' or 'learned')")
         if s.value_mix not in (None, "first", "blend"):
             raise ValueError(f"value_mix {s.value_mix!r} is not known (None, 'first' or 'blend')")
         if s.value_mix is not None and not s.own_kv:
@@ -72,7 +77,9 @@ class PagedAttention(Mixer):
         rot = getattr(s.position, "rotary_dim", 0) if s.position is not None else 0
         if rot > s.head_dim:
             raise ValueError(f"the position encoding rotates {rot} dims, a head has {s.head_dim}")
-        self.q_norm = self.k_norm = self.v_mix = None
+        self.q_norm = self.k_norm = self.v_mix = self.qkv_bias = self.o_bias = self.sink = None
+        # True: whoever combines this mixer's output with others adds `o_bias` (see `output_bias`)
+        self.defer_output_bias = False
 
     def parameters(self):
         s = self.spec
@@ -84,14 +91,25 @@ class PagedAttention(Mixer):
         if s.value_mix is not None:
             out["v_mix"] = ParamSpec((), "float32", "unit")
         if s.qk_norm is not None:
-            out["q_norm"] = ParamSpec((q,), "act", "norm")
+            per_head = s.qk_norm == "per_head"      # one weight of head_dim elements for all heads
+            out["q_norm"] = ParamSpec((s.head_dim if per_head else q,), "act", "norm")
             if s.own_kv:
-                out["k_norm"] = ParamSpec((kv,), "act", "norm")
+                out["k_norm"] = ParamSpec((s.head_dim if per_head else kv,), "act", "norm")
+        if s.bias:
+            out["qkv_bias"] = ParamSpec((rows,), "float32", "bias")
+            out["o_bias"] = ParamSpec((s.hidden_size,), "float32", "bias")
+        if s.sink == "learned":
+            out["sink"] = ParamSpec((s.num_heads,), "float32", "bias")
         return out
 
     def kv_request(self):
         s = self.spec
-        return KVRequest(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim)
+        return KVRequest(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim,
+                         keep_first=int(s.keep_first) if s.window is not None else 0)
+
+    def output_bias(self):
+        """The output projection's bias (32-bit), for a caller that has set ``defer_output_bias``."""
+        return self.o_bias
 
     VALUE_MIX_KEY = "attention.value_mix.first"     # in StepContext.extras: the kept values [tokens, kv heads * value_dim]
 
@@ -123,7 +141,8 @@ class PagedAttention(Mixer):
                             step.seq_rows, slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
                             head_dim=s.head_dim, v_head_dim=s.value_dim, eps=s.qk_norm_eps, page_size=slot.page_size,
                             has_kv=writes, temperature=s.q_temperature, inv_freq=inv_freq, rotary_dim=rotary_dim,
-                            v_first=v_first, v_mix=self.v_mix if v_first is not None else None)
+                            v_first=v_first, v_mix=self.v_mix if v_first is not None else None, bias=self.qkv_bias,
+                            per_head=s.qk_norm == "per_head")
         attn = torch.empty(tokens, s.num_heads * s.value_dim, dtype=x.dtype, device=x.device)
         gate = None
         if s.output_gate:
@@ -132,7 +151,10 @@ class PagedAttention(Mixer):
         # the kernel before the attention is the one that wrote q and this step's keys; it waited for the
         # projection (whose columns the gate is), and the step's inputs are older than both
         self.attend(q, attn, step, slot, after_qk_prep=True, gate=gate)
-        return linear(attn, self.o)
+        y = linear(attn, self.o)
+        if self.o_bias is not None and not self.defer_output_bias:
+            y += self.o_bias.to(y.dtype) if y.dtype != torch.float32 else self.o_bias
+        return y
 
     def forward(self, x, step, slot):
         if self.general:
@@ -180,19 +202,20 @@ class PagedAttention(Mixer):
         ``q``; the split-key kernel then looks its place in the block table up while it still runs.
         ``gate``: the output gate's projection (a view with a row pitch), or None."""
         s = self.spec
-        options = dict(v_head_dim=s.value_dim, softcap=s.score_softcap, sink=s.sink == "zero", gate=gate)
+        sink = self.sink if s.sink == "learned" else s.sink == "zero"
+        options = dict(v_head_dim=s.value_dim, softcap=s.score_softcap, sink=sink, gate=gate, keep_first=s.keep_first)
         if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16
                 and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)
                 and ops.attn_decode_value_dim_supported(s.value_dim)):
             if not self.takes_portion_kernel(step):
-                max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
+                max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window + s.keep_first)
                 ops.attn_decode(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                 num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
                                 page_size=slot.page_size, scale=s.scale, window=s.window, max_keys=max_keys,
                                 step_inputs_settled=after_qk_prep, **options)
             else:
                 # prompt portions: tcgen05 + tensor memory for head size 128 (values as wide), m16n8k16 tiles otherwise
-                fn = (ops.attn_prefill_tc if s.value_dim == s.head_dim
+                fn = (ops.attn_prefill_tc if s.value_dim == s.head_dim and s.sink != "learned" and not s.keep_first
                       and ops.attn_prefill_tc_supported(s.head_dim, s.num_heads, s.num_kv_heads) else ops.attn_prefill)
                 fn(q, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, out, entries=step.num_seqs,
                    max_q_len=step.max_q_len, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
@@ -200,8 +223,7 @@ class PagedAttention(Mixer):
             return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
-                                  page_size=slot.page_size, scale=s.scale, window=s.window, v_head_dim=s.value_dim,
-                                  softcap=s.score_softcap, sink=s.sink == "zero", gate=gate)
+                                  page_size=slot.page_size, scale=s.scale, window=s.window, **options)
 
 
 register_mixer("attention", PagedAttention)

@@ -37,6 +37,8 @@ class KVRequest:
     # "kv": keys and values per KV head.  "latent": one row of head_dim elements per position and
     # nothing else (keys and values are derived from it); num_kv_heads is 1.
     layout: str = "kv"
+    # with a window: the first keep_first positions stay visible (and held) beside the window's
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:

@@ -11,9 +11,12 @@ the one that may ask for pages or state), ``forward(hidden, residual, step, slot
 from ``LayerSpec.extra``.
 
 ``post_norm`` (:class:`PostNormBlock`), ``pre_norm_stream`` (:class:`PreNormStreamBlock`) and
-``sublayer_norm`` (:class:`SublayerNormBlock`) are the arrangements over a 32-bit stream.
+``sublayer_norm`` (:class:`SublayerNormBlock`) are the arrangements over a 32-bit stream,
+``stream_mix`` (:class:`StreamMixBlock`) the one over several such streams.
 """
 from __future__ import annotations
+
+import torch
 
 from .base import make_feed_forward, make_mixer, make_norm
 
@@ -149,7 +152,70 @@ class SublayerNormBlock:
         return hidden, stream
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "post_norm": PostNormBlock, "pre_norm_stream": PreNormStreamBlock,
+class StreamMixBlock:
+    """Pre-norm over several 32-bit residual streams (``parts.streams``): every sublayer reads a learned
+    mixture of the streams through its norm and writes its (optionally gated) result back into all of
+    them.  The block carries ``(pending, streams)``: ``pending = (StreamMix, y, gate logits)`` is the last
+    sublayer's result that the streams have not taken in yet (None at the start); the next sublayer's
+    read applies it in the same kernel.  Whoever needs the streams themselves (the model's last norm, a
+    tap) applies ``pending`` first.  The norms are RMS norms with a 32-bit weight."""
+
+    def __init__(self, spec, dtype):
+        from .streams import StreamMix
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer = make_mixer(spec.mixer, dtype)
+        self.mixer_norm = make_norm(spec.mixer_norm, dtype)
+        if "mixer_streams" not in spec.extra:
+            raise ValueError("a stream_mix block needs extra['mixer_streams'] (a StreamMixSpec)")
+        self.mixer_streams = StreamMix(spec.extra["mixer_streams"], dtype)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_streams = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make_feed_forward(spec.feed_forward, dtype)
+            self.feed_forward_norm = make_norm(spec.feed_forward_norm, dtype)
+            if "feed_forward_streams" not in spec.extra:
+                raise ValueError("a stream_mix block with a feed-forward needs extra['feed_forward_streams']")
+            self.feed_forward_streams = StreamMix(spec.extra["feed_forward_streams"], dtype)
+
+    def parts(self) -> dict:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm, "mixer_streams": self.mixer_streams}
+        if self.feed_forward is not None:
+            out.update({"feed_forward": self.feed_forward, "feed_forward_norm": self.feed_forward_norm,
+                        "feed_forward_streams": self.feed_forward_streams})
+        return out
+
+    @staticmethod
+    def read(streams, pending, mix, norm, dtype):
+        """Apply ``pending`` to the streams and read them for the sublayer whose numbers ``mix`` holds: the
+        normed mixture in the activation type."""
+        from ..csrc import ops
+        h = torch.empty(streams.shape[0], streams.shape[2], dtype=dtype, device=streams.device)
+        write = pending[0].write_args(pending[1], pending[2]) if pending is not None else None
+        if norm.weight.dtype != torch.float32:
+            raise ValueError("a stream_mix block needs norms with a 32-bit weight (RMSNormSpec.offset)")
+        ops.stream_mix(streams, write=write, read=(mix.read_weights(streams.device), norm.weight, norm.spec.eps, h),
+                       dtype=dtype)
+        return h
+
+    def sublayers(self):
+        """(name, run(h, step, slot), StreamMix, norm) of each sublayer, in order."""
+        out = [("mixer." + self.mixer.spec.kind, lambda h, step, slot: self.mixer.forward(h, step, slot),
+                self.mixer_streams, self.mixer_norm)]
+        if self.feed_forward is not None:
+            out.append(("feed_forward." + self.feed_forward.spec.kind, lambda h, step, slot: self.feed_forward.forward(h, step),
+                        self.feed_forward_streams, self.feed_forward_norm))
+        return out
+
+    def forward(self, pending, streams, step, slot, timed=None):
+        run = timed if timed is not None else (lambda name, fn, *a: fn(*a))
+        for name, sub, mix, norm in self.sublayers():
+            h = run("stream_mix", self.read, streams, pending, mix, norm, self.dtype)
+            y = run(name, sub, h, step, slot)
+            pending = (mix, y, run("stream_gate", mix.gate_logits, h))
+        return pending, streams
+
+
+ARRANGEMENTS = {"stream_mix": StreamMixBlock, "pre_norm": PreNormBlock, "post_norm": PostNormBlock, "pre_norm_stream": PreNormStreamBlock,
                 "sublayer_norm": SublayerNormBlock}
 
 

@@ -87,6 +87,10 @@ class _RoutedSwiGLU(FeedForward):
     # many experts' weights a step had to read.
     route_stats = None
 
+    # experts without weights whose output is their input: ids from num_experts on (the routing build gives
+    # them no row; the sum over the slots adds weight * x for them)
+    identity_experts = 0
+
     def run_experts(self, x, ids, weights, add=None):
         """``add``: a [tokens, hidden] tensor that joins the 32-bit sum over the slots before it is rounded."""
         tokens = x.shape[0]
@@ -98,7 +102,9 @@ class _RoutedSwiGLU(FeedForward):
         max_tiles = ops.moe_max_tiles(a, self.num_experts, tile_rows)
         i32 = dict(dtype=torch.int32, device=dev)
         ws = {"counts": torch.empty(self.num_experts, **i32), "rank": torch.empty(a, **i32),
-              "offsets": torch.empty(self.num_experts + 1, **i32), "sorted": torch.empty(a, **i32),
+              "offsets": torch.empty(self.num_experts + 1, **i32),
+              # with identity experts fewer than `a` places are filled; the gather of rows reads all of them
+              "sorted": (torch.zeros if self.identity_experts else torch.empty)(a, **i32),
               "inv_pos": torch.empty(a, **i32), "tile_expert": torch.empty(max_tiles, **i32),
               "tile_row0": torch.empty(max_tiles, **i32), "num_tiles": torch.empty(1, **i32)}
         # the tensor-core GEMM reads the activation rows in expert order
@@ -133,7 +139,8 @@ class _RoutedSwiGLU(FeedForward):
             ops.moe_grouped_gemm_plain(1, act, self.w2, ws, weights, y, max_tiles=max_tiles, n_out=self.hidden,
                                        k_dim=self.inter, top_k=self.top_k)
         out = torch.empty(tokens, self.hidden, dtype=x.dtype, device=dev)
-        ops.moe_combine(y, ws["inv_pos"], out, self.top_k, add=add)
+        ops.moe_combine(y, ws["inv_pos"], out, self.top_k, add=add,
+                        identity=(x, weights) if self.identity_experts else None)
         return out
 
 
@@ -155,7 +162,7 @@ class SparseMoE(_RoutedSwiGLU):
             self.shared = DenseMLP(spec.shared, dtype)
         if spec.score_fn not in ops.SCORE_FN:
             raise ValueError(f"score function {spec.score_fn!r} is not supported")
-        if not 0 < spec.top_k <= spec.num_experts:
+        if not 0 < spec.top_k <= spec.num_experts + max(0, int(spec.identity_experts)):
             raise ValueError("top_k must be in [1, num_experts]")
         most = min(ops.LIMITS["router_max_experts"], ops.LIMITS["moe_max_experts"])
         if spec.num_experts > most:
@@ -168,6 +175,10 @@ class SparseMoE(_RoutedSwiGLU):
             raise ValueError("hidden_size and intermediate_size must be positive")
         self.num_experts, self.top_k = spec.num_experts, spec.top_k
         self.hidden, self.inter = spec.hidden_size, spec.intermediate_size
+        self.identity_experts = int(spec.identity_experts)
+        if self.identity_experts < 0 or (self.identity_experts and (spec.groups > 1 or spec.score_fn == "top_softmax")):
+            raise ValueError("identity experts need a plain selection by scores (no groups, not 'top_softmax')")
+        self.routed = spec.num_experts + self.identity_experts      # the router's outputs
         self.selection_bias = None
 
     def bind(self, tensors):
@@ -179,11 +190,11 @@ class SparseMoE(_RoutedSwiGLU):
 
     def parameters(self):
         s = self.spec
-        out = {"gate": ParamSpec((s.num_experts, s.hidden_size), "float32"),
+        out = {"gate": ParamSpec((self.routed, s.hidden_size), "float32"),
                "w13": ParamSpec((s.num_experts, 2 * s.intermediate_size, s.hidden_size)),
                "w2": ParamSpec((s.num_experts, s.hidden_size, s.intermediate_size))}
         if s.selection_bias:
-            out["selection_bias"] = ParamSpec((s.num_experts,), "float32", "bias")
+            out["selection_bias"] = ParamSpec((self.routed,), "float32", "bias")
         if self.shared is not None:
             for name, p in self.shared.parameters().items():
                 out["shared_" + name] = p
@@ -222,7 +233,7 @@ class SparseMoE(_RoutedSwiGLU):
                 mid = rest.to(torch.bfloat16)
                 lo = (rest - mid.float()).to(torch.bfloat16)
                 split = torch.cat([hi, mid, lo], 0)                                   # [3E, H]
-                self._gate_split = split.view(3 * self.num_experts, chunks, h // chunks).permute(1, 2, 0).contiguous()
+                self._gate_split = split.view(3 * self.routed, chunks, h // chunks).permute(1, 2, 0).contiguous()
         return self._gate_split if self._gate_split is not False else None
 
     def route(self, x):
@@ -238,7 +249,7 @@ class SparseMoE(_RoutedSwiGLU):
             chunks, kc, _ = split.shape
             parts = torch.bmm(x.view(tokens, chunks, kc).transpose(0, 1), split, out_dtype=torch.float32)
             # the selection adds the parts itself (chunk by chunk, term by term)
-            ops.router_select(parts.view(chunks, tokens, 3, self.num_experts), self.selection_bias, ids, weights,
+            ops.router_select(parts.view(chunks, tokens, 3, self.routed), self.selection_bias, ids, weights,
                               top_k=self.top_k, score_fn=s.score_fn, renormalize=s.renormalize,
                               routed_scale=s.routed_scale, groups=s.groups, keep_groups=s.keep_groups)
         else:

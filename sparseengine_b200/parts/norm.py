@@ -23,7 +23,14 @@ class RMSNorm(Norm):
             raise ValueError("RMSNorm eps must be positive")
 
     def parameters(self):
+        if self.spec.offset:        # kept in 32-bit: offset + w would lose the stored digits in a 16-bit type
+            return {"weight": ParamSpec((self.spec.size,), "float32", "bias")}
         return {"weight": ParamSpec((self.spec.size,), "act", "norm")}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        if self.spec.offset:
+            self.weight = self.weight + float(self.spec.offset)     # what the kernels multiply by
 
     def forward(self, x, residual=None):
         out = torch.empty_like(x)

@@ -81,14 +81,20 @@ class GatedDeltaMixer(Mixer):
     k unit vectors per head (q times ``head_dim ** -0.5``); ``beta = sigmoid(b)``; decay per head and key
     channel ``exp(-exp(A_log) softplus(a2(a) + dt_bias))``; per head ``S <- diag(decay) S``,
     ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q``; each head's ``o`` over its root
-    mean square, times a weight shared by the heads, times ``sigmoid(g2(g))``; out projection."""
+    mean square, times a weight shared by the heads, times ``sigmoid(g2(g))``; out projection.
+    With ``decay_per="head"`` the decay is one number per head, ``exp(-exp(A_log) softplus(a + dt_bias))``
+    with ``a`` a column of the input projection, and the gate ``gate_activation(g)`` with ``g`` columns of
+    the input projection (no low ranks)."""
     graph_safe = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         s = spec
-        if min(s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.conv_taps, s.decay_rank, s.gate_rank,
-               s.hidden_size) <= 0:
+        if s.decay_per not in ("channel", "head") or s.gate_activation not in ("sigmoid", "silu"):
+            raise ValueError("decay_per is 'channel' or 'head', gate_activation 'sigmoid' or 'silu'")
+        self.per_head = s.decay_per == "head"
+        ranks = () if self.per_head else (s.decay_rank, s.gate_rank)
+        if min(s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.conv_taps, s.hidden_size, *ranks) <= 0:
             raise ValueError("the sizes of a gated-delta mixer must be positive")
         if s.num_heads % s.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
@@ -101,18 +107,23 @@ class GatedDeltaMixer(Mixer):
         self.conv_off = s.num_heads * s.v_head_dim * s.head_dim
         self.b_off = self.conv_channels
         self.a_off = self.b_off + s.num_heads
-        self.g_off = self.a_off + s.decay_rank
+        # one decay per head: the decay's and the gate's columns come straight from the input projection
+        self.a_cols = s.num_heads if self.per_head else s.decay_rank
+        self.g_off = self.a_off + self.a_cols
+        self.g_cols = self.vv if self.per_head else s.gate_rank
 
     def parameters(self):
         s = self.spec
-        return {"in_proj": ParamSpec((self.g_off + s.gate_rank, s.hidden_size)),
-                "conv_w": ParamSpec((self.conv_channels, s.conv_taps), "float32"),
-                "a2": ParamSpec((s.num_heads * s.head_dim, s.decay_rank)),
-                "g2": ParamSpec((self.vv, s.gate_rank)),
-                "dt_bias": ParamSpec((s.num_heads * s.head_dim,), "float32", "bias"),
-                "a_log": ParamSpec((s.num_heads,), "float32", "bias"),
-                "norm_w": ParamSpec((s.v_head_dim,), "float32", "norm"),
-                "o": ParamSpec((s.hidden_size, self.vv))}
+        out = {"in_proj": ParamSpec((self.g_off + self.g_cols, s.hidden_size)),
+               "conv_w": ParamSpec((self.conv_channels, s.conv_taps), "float32"),
+               "dt_bias": ParamSpec((s.num_heads * (1 if self.per_head else s.head_dim),), "float32", "bias"),
+               "a_log": ParamSpec((s.num_heads,), "float32", "bias"),
+               "norm_w": ParamSpec((s.v_head_dim,), "float32", "norm"),
+               "o": ParamSpec((s.hidden_size, self.vv))}
+        if not self.per_head:
+            out["a2"] = ParamSpec((s.num_heads * s.head_dim, s.decay_rank))
+            out["g2"] = ParamSpec((self.vv, s.gate_rank))
+        return out
 
     def state_request(self):
         return StateRequest((self.conv_off + (self.spec.conv_taps - 1) * self.conv_channels,), torch.float32)
@@ -123,18 +134,20 @@ class GatedDeltaMixer(Mixer):
         proj = linear(x, self.in_proj)
         qkv = torch.empty(tokens, self.conv_channels, dtype=torch.float32, device=dev)
         ops.causal_conv(proj, 0, self.conv_w, None, slot.state, self.conv_off, step, qkv)
-        a = linear(proj[:, self.a_off:self.a_off + s.decay_rank], self.a2)
-        gate = linear(proj[:, self.g_off:self.g_off + s.gate_rank], self.g2)
+        a, gate = proj[:, self.a_off:self.a_off + self.a_cols], proj[:, self.g_off:self.g_off + self.g_cols]
+        if not self.per_head:       # through the low ranks
+            a, gate = linear(a, self.a2), linear(gate, self.g2)
         dec = torch.empty(tokens, s.num_heads * s.head_dim, dtype=torch.float32, device=dev)
         beta = torch.empty(tokens, s.num_heads, dtype=torch.float32, device=dev)
         ops.delta_prep(qkv, a, proj, self.b_off, self.dt_bias, self.a_log, dec, beta, heads=s.num_heads,
                        kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim, unit_eps=s.unit_eps,
-                       q_scale=s.head_dim ** -0.5)
+                       q_scale=s.head_dim ** -0.5, per_head=self.per_head)
         o = torch.empty(tokens, self.vv, dtype=torch.float32, device=dev)
         ops.delta_scan(qkv, dec, beta, slot.state, step, o, heads=s.num_heads, kv_heads=s.num_kv_heads,
                        head_dim=s.head_dim, v_head_dim=s.v_head_dim)
         out = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
-        ops.delta_out(o, gate, self.norm_w, out, v_head_dim=s.v_head_dim, eps=s.norm_eps)
+        ops.delta_out(o, gate, self.norm_w, out, heads=s.num_heads, v_head_dim=s.v_head_dim, eps=s.norm_eps,
+                      silu=s.gate_activation == "silu")
         return linear(out, self.o)
 
 
@@ -205,6 +218,58 @@ class RetentionMixer(Mixer):
         return linear(gated, self.o)
 
 
+class MatrixMemoryMixer(Mixer):
+    """``[q | k | v | g | i | f] = in_proj(h)``; per head a matrix memory with exponential gates held stable
+    by a running maximum (``config.specs.MatrixMemorySpec``; kernels: csrc/matrix_memory.cu).  The state is
+    one 32-bit row per request: ``[heads, head_dim, v_head_dim + 1]`` (the normaliser is the last column),
+    then the maximum per head."""
+    graph_safe = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        s = spec
+        if min(s.num_heads, s.head_dim, s.v_head_dim, s.hidden_size) <= 0 or not s.gate_cap > 0:
+            raise ValueError("the sizes and the gate cap of a matrix memory must be positive")
+        if s.head_dim > ops.LIMITS["memory_max_head_dim"]:
+            raise ValueError(f"head_dim {s.head_dim} is not supported (at most {ops.LIMITS['memory_max_head_dim']}: "
+                             "a state column's rows live in the registers of eight warps)")
+        if s.num_heads > ops.LIMITS["grid_dim_yz"]:
+            raise ValueError("heads are a grid dimension of the kernels (at most 65,535)")
+        self.qk = s.num_heads * s.head_dim
+        self.vv = s.num_heads * s.v_head_dim
+        self.g_off = 2 * self.qk + self.vv
+        self.i_off = self.g_off + self.vv
+        self.f_off = self.i_off + s.num_heads
+        self.m_off = s.num_heads * s.head_dim * (s.v_head_dim + 1)
+        self.out_scale = 1.0        # a caller that weighs this mixer's output may fold the weight in here
+
+    def parameters(self):
+        s = self.spec
+        return {"in_proj": ParamSpec((self.f_off + s.num_heads, s.hidden_size)),
+                "gate_bias": ParamSpec((2 * s.num_heads,), "float32", "bias"),       # input gates, then forget gates
+                "norm_w": ParamSpec((self.vv,), "float32", "norm"),
+                "o": ParamSpec((s.hidden_size, self.vv))}
+
+    def state_request(self):
+        return StateRequest((self.m_off + self.spec.num_heads,), torch.float32)
+
+    def forward(self, x, step, slot):
+        s = self.spec
+        tokens, dev = x.shape[0], x.device
+        proj = linear(x, self.in_proj)
+        gates = torch.empty(tokens, s.num_heads, 3, dtype=torch.float32, device=dev)
+        ops.memory_gates(proj, self.i_off, self.f_off, self.gate_bias, s.gate_cap, slot.state, self.m_off, step, gates,
+                         heads=s.num_heads)
+        o = torch.empty(tokens, s.num_heads, s.v_head_dim + 1, dtype=torch.float32, device=dev)
+        ops.memory_scan(proj, 0, self.qk, 2 * self.qk, gates, s.head_dim ** -0.5, slot.state, step, o, heads=s.num_heads,
+                        head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        gated = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
+        ops.memory_out(o, gates, proj, self.g_off, self.norm_w, gated, heads=s.num_heads, v_head_dim=s.v_head_dim,
+                       eps=s.norm_eps, den_eps=s.den_eps)
+        return linear(gated, self.o)
+
+
+register_mixer("matrix_memory", MatrixMemoryMixer)
 register_mixer("retention", RetentionMixer)
 register_mixer("mamba2", StateSpaceMixer)
 register_mixer("channel_delta", GatedDeltaMixer)
