@@ -482,13 +482,15 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-long-context", action="store_true", help="leave out the 131,072-token point")
     ap.add_argument("--long-layers", type=int, default=LONG_LAYERS)
-    ap.add_argument("--design", default="minimax_m2", choices=["minimax_m2", "hybrid", "zisevik", "kisusun"],
+    ap.add_argument("--design", default="minimax_m2", choices=["minimax_m2", "hybrid", "zisevik", "kisusun", "tedisun"],
                     help="hybrid: prefill and decode throughput of the hybrid design (attention, state-space and "
                          "gated-delta mixers) at two layer sizes beside MiniMax M2 layers of equal width, and its "
                          "kernels alone against their rooflines, instead of the headline workload; zisevik: the same "
                          "for the Zisevik design (latent attention, retention, a looped stack) beside the hybrid design; kisusun: "
                          "the same for the Kisusun design (capped, gated attention with a sink and blended values, grouped "
-                         "routing with a shared expert) beside MiniMax M2 layers")
+                         "routing with a shared expert) beside MiniMax M2 layers; tedisun: the same for the Tedisun design "
+                         "(several residual streams, a delta rule with one decay per head, attention with kept first keys and "
+                         "a learned sink beside a matrix memory, identity experts) beside the Zisevik design")
     ap.add_argument("--only-decode", action="store_true",
                     help="time the headline decode only (no points, prefill or end-to-end run): for profiling")
     args = ap.parse_args()
@@ -516,6 +518,10 @@ def main() -> int:
     if args.design == "zisevik":
         from sparseengine_b200.cli import zisevik_bench
         print(json.dumps(zisevik_bench.run(steps=min(args.steps, 20), warmup=args.warmup)))
+        return 0
+    if args.design == "tedisun":
+        from sparseengine_b200.cli import tedisun_bench
+        print(json.dumps(tedisun_bench.run(steps=min(args.steps, 20), warmup=args.warmup)))
         return 0
     if args.design == "kisusun":
         from sparseengine_b200.cli import kisusun_bench

@@ -226,3 +226,75 @@ def forward(config, w, tokens, layers_out=None):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits
+
+
+# ---- random weights ----------------------------------------------------------------------------
+
+def random_weights(config, seed):
+    """Checkpoint tensors (bfloat16) for ``config``, spread so that every mechanism matters."""
+    g = torch.Generator().manual_seed(seed)
+    W, V, S = config["width"], config["vocab"], int(config.get("streams", 1))
+    out = {}
+
+    def put(name, shape, std=1.0, mean=0.0):
+        out[name] = (torch.randn(*shape, generator=g) * std + mean).to(torch.bfloat16)
+
+    def lin(name, rows, cols, gain=1.0):
+        put(name, (rows, cols), gain * cols ** -0.5)
+
+    put("embed", (V, W), W ** -0.5)
+    lin("head", V, W)
+    put("final.norm", (W,), 0.1)
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        subs = (1, 2) if layer.get("mlp") is not None else (1,)
+        for q in subs:
+            put(f"{p}norm{q}", (W,), 0.1)
+            if "streams" in config:
+                put(f"{p}hc{q}.in", (S,), 0.2, 1.0 / S)
+                put(f"{p}hc{q}.out", (S,), 0.3, 0.8)
+                out[f"{p}hc{q}.mix"] = (torch.eye(S) + 0.15 * torch.randn(S, S, generator=g)).to(torch.bfloat16)
+            lin(f"{p}rg{q}", W, W)
+            put(f"{p}rg{q}.b", (W,), 0.5, 0.5)
+        if layer["type"] == "delta":
+            H, G, d, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for name, rows in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                lin(p + "mix." + name, rows, W, 2.0)
+                put(p + "mix." + name + ".conv", (rows, taps), 0.6)
+            lin(p + "mix.b", H, W)
+            lin(p + "mix.a", H, W)
+            put(p + "mix.A_log", (H,), 0.7, -1.0)
+            put(p + "mix.dt_bias", (H,), 0.7, -1.0)
+            put(p + "mix.norm", (dv,), 0.1, 1.0)
+            lin(p + "mix.g", H * dv, W)
+            lin(p + "mix.o", W, H * dv)
+        else:
+            a, r = m["left"], m["right"]
+            H, G, d, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            for name, rows in (("q", H * d), ("k", G * d), ("v", G * dv)):
+                lin(p + "mix.left." + name, rows, W)
+                put(p + "mix.left." + name + ".b", (rows,), 0.3)
+            put(p + "mix.left.q.norm", (d,), 0.2, 1.0)
+            put(p + "mix.left.k.norm", (d,), 0.2, 1.0)
+            put(p + "mix.left.sink", (H,), 1.0)
+            lin(p + "mix.left.o", W, H * dv)
+            put(p + "mix.left.o.b", (W,), 0.2)
+            H, d, dv = r["heads"], r["dim"], r["vdim"]
+            for name, rows in (("q", H * d), ("k", H * d), ("v", H * dv), ("g", H * dv)):
+                lin(p + "mix.right." + name, rows, W)
+            lin(p + "mix.right.o", W, H * dv)
+            put(p + "mix.right.norm", (H * dv,), 0.1, 1.0)
+            lin(p + "mix.right.i", H, W, 2.0)
+            put(p + "mix.right.i.b", (H,), 1.0)
+            lin(p + "mix.right.f", H, W, 2.0)
+            put(p + "mix.right.f.b", (H,), 1.0, 2.0)
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            E, ident, ff = mlp["router"]["experts"], mlp["router"].get("identity", 0), mlp["expert"]["ff"]
+            for e in range(E):
+                lin(f"{p}mlp.e{e}.gate", ff, W)
+                lin(f"{p}mlp.e{e}.up", ff, W)
+                lin(f"{p}mlp.e{e}.down", W, ff)
+            lin(p + "mlp.router", E + ident, W, 2.0)
+            put(p + "mlp.correction", (E + ident,), 0.05)
+    return out
