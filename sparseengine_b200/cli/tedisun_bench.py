@@ -126,6 +126,9 @@ def _kernels(width: int, cases, pk: dict) -> dict:
             add("like: attn_prefill (window, sink of 0)", lambda: ops.attn_prefill(
                 q, cache, table, step.seq_rows, step.cu_q, kv_len, o, entries=entries, max_q_len=per, sink=True, **att),
                 flops=4.0 * seen * hq * d)
+            add("attn_prefill_tc (window, kept first keys, learned sink)", lambda: ops.attn_prefill_tc(
+                q, cache, table, step.seq_rows, step.cu_q, kv_len, o, entries=entries, max_q_len=per, sink=sink, keep_first=KEPT, **att),
+                flops=4.0 * seen * hq * d)
             add("like: attn_prefill_tc (window, sink of 0)", lambda: ops.attn_prefill_tc(
                 q, cache, table, step.seq_rows, step.cu_q, kv_len, o, entries=entries, max_q_len=per, sink=True, **att),
                 flops=4.0 * seen * hq * d)

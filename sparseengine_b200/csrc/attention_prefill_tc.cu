@@ -176,7 +176,12 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int k_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
     const int k_begin = (k_lo / kKeys) * kKeys;
     const int k_end = max_pos + 1;
-    const int num_tiles = (k_end - k_begin + kKeys - 1) / kKeys;
+    // first keys that stay visible beside a window: those before the CTA's window come as tiles of their own, ahead
+    // of the window's (tile j < kept_tiles holds keys 64 j .., of which those below `kept` are read)
+    const int keep_first = window > 0 ? opt.keep_first : 0;
+    const int kept = min(keep_first, k_lo);
+    const int kept_tiles = (kept + kKeys - 1) / kKeys;
+    const int num_tiles = kept_tiles + (k_end - k_begin + kKeys - 1) / kKeys;
 
     auto bar = [&](uint64_t* b) { return smem_u32(b); };
     if (threadIdx.x == 0) {
@@ -223,6 +228,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const size_t head_off = (size_t)kvh * page_size * D;
     const size_t v_off = (size_t)hkv * page_size * D;
 
+    const int k_lo_window = k_lo, k_end_window = k_end;
     if (warp == 0 || warp == kLoaderWarp2) {
         // ---- loaders: K/V tiles from their pages ------------------------------------------
         // Lane l looks up where keys base+l and base+32+l live (two independent table loads per
@@ -230,7 +236,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         // between the asynchronous copies.
         auto issue = [&](int tile) {
             uint8_t* st = kv_s + (size_t)(tile % kStages) * kKVStageBytes;
-            const int base = k_begin + tile * kKeys;
+            const bool first = tile < kept_tiles;
+            const int base = first ? tile * kKeys : k_begin + (tile - kept_tiles) * kKeys;
+            const int k_lo = first ? 0 : k_lo_window, k_end = first ? kept : k_end_window;      // the keys of this tile that are read
             // Keys outside [k_lo, k_end) are zero-filled, never read: a page the window has left
             // behind may belong to another request by now.  An entry that names no page of the pool
             // is not followed either (address 0 marks its row; a code goes to the error word).
@@ -344,16 +352,20 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));    // non-negative floats order as integers
                 se::mma::cap_scores_by<64>(reinterpret_cast<float*>(sv), __uint_as_float(wmax) * opt.cap_in, opt.cap_in, opt.cap_out);
             }
-            const int key0 = k_begin + j * kKeys;
+            const bool first = j < kept_tiles;
+            const int key0 = first ? j * kKeys : k_begin + (j - kept_tiles) * kKeys;
             // A tile every row of the warp sees in full needs no masking (rows ascend with the
-            // lane: lane 0 has the smallest position, lane 31 the largest window start).
-            const bool full = key0 + kKeys - 1 <= __shfl_sync(0xffffffffu, pos, 0) &&
-                              key0 >= __shfl_sync(0xffffffffu, lo, 31);
+            // lane: lane 0 has the smallest position, lane 31 the largest window start).  A tile of kept first keys
+            // is seen by every row as far as it holds such keys; in a window's tile a key before the row's window is
+            // seen if it is a kept one that no tile of kept keys has brought.
+            const bool full = first ? key0 + kKeys <= kept
+                                    : key0 + kKeys - 1 <= __shfl_sync(0xffffffffu, pos, 0) &&
+                                          key0 >= __shfl_sync(0xffffffffu, lo, 31) && key0 >= kept;
             if (!full) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int key = key0 + c;
-                    if (key > pos || key < lo) sv[c] = 0xff800000u;      // -inf
+                    if (first ? key >= kept : (key > pos || (key < lo && key >= keep_first) || key < kept)) sv[c] = 0xff800000u;      // -inf
                 }
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
@@ -419,7 +431,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         if (ok && mbar_wait(bar(&bars.o_done[x]), 0, &abort_s)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // the sink's term 2^(0 - m): it grows beyond the type only where the keys hold nothing (the output is 0 then)
-            if (opt.sink) l += exp2f(-m_ref);
+            if (opt.sink) l += exp2f(se::mma::sink_log2(opt, kvh * group + rr % group) - m_ref);
             const float inv = 1.f / l;
             __nv_bfloat16* dst = out + ((size_t)(tok0 + rr / group) * hq + kvh * group + rr % group) * D;
             const bool gate_vec = opt.gate != nullptr && se::mma::gate_rows_aligned(opt, 16);
@@ -480,13 +492,15 @@ extern "C" int se_attn_prefill_tc(const void* q, const void* cache, const int* t
                                   const int* seq_rows, const int* cu_q, const int* kv_len, void* out, int* error,
                                   int entries, int max_q_len, int hq, int hkv, int head_dim, int page_size, float scale,
                                   int window, int num_pages, float softcap, int sink, const void* gate, int gate_pitch,
-                                  cudaStream_t stream) {
+                                  const float* sink_logits, int keep_first, cudaStream_t stream) {
     using namespace se::fa;
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!se_attn_prefill_tc_supported(head_dim, hq, hkv) || entries > 65535 || hkv > 65535) return SE_ERR_UNSUPPORTED;
-    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * head_dim)) return SE_ERR_ARGUMENT;
-    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink,
-                                      (const __nv_bfloat16*)gate, gate_pitch};
+    if (softcap < 0.f || !(scale > 0.f) || (gate != nullptr && gate_pitch < hq * head_dim) || keep_first < 0)
+        return SE_ERR_ARGUMENT;
+    const se::mma::SoftmaxOptions opt{softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f,
+                                      sink || sink_logits != nullptr, (const __nv_bfloat16*)gate, gate_pitch, sink_logits,
+                                      window > 0 ? keep_first : 0};
     const size_t smem = (size_t)kTiles * kQBytes + kStages * kKVStageBytes + 1024;
     static bool configured = false;
     if (!configured) {

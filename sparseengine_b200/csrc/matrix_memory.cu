@@ -10,7 +10,8 @@
 //
 // n is kept as one more column of S (a value column of ones), so the state row of a request is
 // [head][d][dv + 1] followed by m [head].  Three kernels: the gates (the scalar recurrence of m, a warp
-// per request and head, 32 tokens at a time by prefix sum and prefix maximum), the matrix recurrence,
+// per request and head, 32 tokens at a time by prefix sum and prefix maximum), the matrix recurrence
+// (token by token for steps of single tokens, in chunks of 64 tokens for prompt portions),
 // and the epilogue (denominator, each head's root mean square, weight, sigmoid gate).  q, k, v and the
 // gate come from the projection in the activation type; everything else is 32-bit.
 //
@@ -22,7 +23,8 @@ namespace se {
 
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// gates[t][h] = (keep, take, exp(-m_t)); the request's m is brought up to date.  One warp per (entry, head).
+// gates[t][h] = (log keep, log take, exp(-m_t)) with keep = exp(f_t + m_(t-1) - m_t) and take = exp(i_t - m_t);
+// the request's m is brought up to date.  One warp per (entry, head).
 template <typename T>
 __global__ void memory_gates_kernel(const T* proj, int pitch, int i_off, int f_off, const float* __restrict__ bias,
                                     float cap, float* state, long long state_pitch, int m_off,
@@ -60,8 +62,8 @@ __global__ void memory_gates_kernel(const T* proj, int pitch, int i_off, int f_o
         if (lane == 0) m_prev = m_in;
         if (valid) {
             float* g = gates + ((size_t)t * H + h) * 3;
-            g[0] = expf(gf + m_prev - m);
-            g[1] = expf(gi - m);
+            g[0] = gf + m_prev - m;
+            g[1] = gi - m;
             g[2] = expf(-m);
         }
         const int last = min(31, t1 - 1 - base);
@@ -108,13 +110,13 @@ memory_scan_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, co
             const int tt = x / d, i = x - tt * d;
             const T* row = proj + (size_t)(tb + tt) * pitch;
             qs[x] = to_float(row[q_off + h * d + i]) * q_scale;
-            ks[x] = to_float(row[k_off + h * d + i]) * gates[((size_t)(tb + tt) * H + h) * 3 + 1];
+            ks[x] = to_float(row[k_off + h * d + i]) * expf(gates[((size_t)(tb + tt) * H + h) * 3 + 1]);
         }
         for (int x = threadIdx.x; x < nt * 32; x += blockDim.x) {
             const int tt = x >> 5, c = c0 + (x & 31);
             vs[x] = c < dv ? to_float(proj[(size_t)(tb + tt) * pitch + v_off + h * dv + c]) : (c == dv ? 1.f : 0.f);
         }
-        if ((int)threadIdx.x < nt) keep[threadIdx.x] = gates[((size_t)(tb + threadIdx.x) * H + h) * 3];
+        if ((int)threadIdx.x < nt) keep[threadIdx.x] = expf(gates[((size_t)(tb + threadIdx.x) * H + h) * 3]);
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float v = vs[tt * 32 + lane], g = keep[tt];
@@ -145,6 +147,160 @@ memory_scan_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, co
         const int i = warp + kMemWarps * n;
         if (i < d && col_ok) S[(size_t)i * cols + col] = st[n];
     }
+}
+
+// ---- prompt portions: the recurrence in chunks of 64 tokens -----------------------------------------
+//
+// With B_t the sum of the log keeps of a chunk's tokens 0..t and l_s the log take of token s, the recurrence
+// over a chunk of n tokens has a closed form:
+//
+//     o_t   = exp(B_t) S_0^T q_t + sum_{s <= t} exp(B_t - B_s + l_s) (q_t . k_s) [v_s | 1]
+//     S_new = exp(B_(n-1)) S_0 + sum_s exp(B_(n-1) - B_s + l_s) k_s [v_s | 1]^T
+//
+// which is three small matrix products per chunk instead of a chain of n dependent steps; every exponent
+// is at most 0 (the running maximum sees to that).  All of it is 32-bit FMA arithmetic; the sums B are taken
+// in 64-bit, so that their differences keep the digits of the single terms.  One block per (entry, head,
+// 32 columns of [values | 1]): q and k of the chunk lie transposed in shared memory (`[dim][token]`, padded
+// rows), the block's slice of the state stays in shared memory over all chunks.
+constexpr int kChunk = 64;
+constexpr int kChunkThreads = 256;
+constexpr int kPitch = kChunk + 4;
+__device__ __forceinline__ int swz(int i, int t) { return i * kPitch + t; }
+
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads, 2)
+memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, const float* __restrict__ gates,
+                    float q_scale, float* state, long long state_pitch, const int* __restrict__ cu_q,
+                    const int* __restrict__ seq_rows, float* __restrict__ o, int H, int d, int dv) {
+    extern __shared__ __align__(16) float chunk_smem[];
+    float* qs = chunk_smem;                      // [d][kPitch]
+    float* ks = qs + d * kPitch;                 // [d][kPitch]
+    float* vs = ks + d * kPitch;                 // [64][32]
+    float* As = vs + kChunk * 32;                // [64 s][64 t]: exp(B_t - B_s + l_s) q_t . k_s for s <= t, else 0
+    float* Ss = As + kChunk * kChunk;            // [d][32]
+    float* ls = Ss + d * 32;                     // [64] log takes
+    double* Bs = reinterpret_cast<double*>(ls + kChunk);      // [64] sums of the log keeps (8-byte aligned: every part before is a multiple of 8 bytes)
+    const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
+    const int cols = dv + 1;
+    const int t_first = cu_q[e], t_last = cu_q[e + 1];
+    if (t_last <= t_first) return;
+    float* S = state + (size_t)seq_rows[e] * state_pitch + (size_t)h * d * cols;
+    const bool col_ok = c0 + lane < cols;
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
+        Ss[x] = c0 + (x & 31) < cols ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+
+    for (int tb = t_first; tb < t_last; tb += kChunk) {
+        const int n = min(kChunk, t_last - tb);
+        __syncthreads();                          // the chunk before is done with q, k, v and A; the state is up to date
+        for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
+            const int t = x / d, i = x - t * d;
+            float qv = 0.f, kv = 0.f;
+            if (t < n) {
+                const T* row = proj + (size_t)(tb + t) * pitch;
+                qv = to_float(row[q_off + h * d + i]) * q_scale;
+                kv = to_float(row[k_off + h * d + i]);
+            }
+            qs[swz(i, t)] = qv;
+            ks[swz(i, t)] = kv;
+        }
+        for (int x = threadIdx.x; x < kChunk * 32; x += kChunkThreads) {
+            const int t = x >> 5, c = c0 + (x & 31);
+            vs[x] = t < n ? (c < dv ? to_float(proj[(size_t)(tb + t) * pitch + v_off + h * dv + c]) : (c == dv ? 1.f : 0.f)) : 0.f;
+        }
+        if (wg == 0) {                            // the sums of the log keeps, 64-bit, by one warp
+            double carry = 0.0;
+            for (int half = 0; half < 2; ++half) {
+                const int t = half * 32 + lane;
+                const float* g = gates + ((size_t)(tb + t) * H + h) * 3;
+                double b = t < n ? (double)g[0] : 0.0;
+                ls[t] = t < n ? g[1] : -INFINITY;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const double v = __shfl_up_sync(0xffffffffu, b, off);
+                    if (lane >= off) b += v;
+                }
+                b += carry;
+                Bs[t] = b;
+                carry = __shfl_sync(0xffffffffu, b, 31);
+            }
+        }
+        __syncthreads();
+        // scores of the chunk with their weights: a 4 x 4 tile per thread, tiles above the diagonal are zero
+        {
+            const int tt = (threadIdx.x >> 4) * 4, ss = (threadIdx.x & 15) * 4;
+            float acc[4][4] = {};
+            if (ss <= tt + 3) {
+#pragma unroll 4
+                for (int i = 0; i < d; ++i) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + swz(i, tt));
+                    const float4 kv = *reinterpret_cast<const float4*>(ks + swz(i, ss));
+                    const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                    for (int a = 0; a < 4; ++a)
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) acc[a][b] += qa[a] * ka[b];
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                float4 row;
+                float* r = &row.x;
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+                    r[a] = (ss + b <= tt + a && tt + a < n) ? acc[a][b] * expf((float)(Bs[tt + a] - Bs[ss + b]) + ls[ss + b]) : 0.f;
+                *reinterpret_cast<float4*>(As + (ss + b) * kChunk + tt) = row;
+            }
+        }
+        float vreg[kChunk];                        // this lane's value column of the chunk
+#pragma unroll
+        for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] = vs[s_ * 32 + lane];
+        __syncthreads();
+        // outputs: warp wg takes tokens 8 wg .. 8 wg + 7, lane c the column
+        {
+            const int tg = wg * 8;
+            float acc[8] = {}, acc2[8] = {};
+#pragma unroll
+            for (int s_ = 0; s_ < kChunk; ++s_) {
+                const float4 a0 = *reinterpret_cast<const float4*>(As + s_ * kChunk + tg);
+                const float4 a1 = *reinterpret_cast<const float4*>(As + s_ * kChunk + tg + 4);
+                const float v = vreg[s_];
+                acc[0] += a0.x * v; acc[1] += a0.y * v; acc[2] += a0.z * v; acc[3] += a0.w * v;
+                acc[4] += a1.x * v; acc[5] += a1.y * v; acc[6] += a1.z * v; acc[7] += a1.w * v;
+            }
+#pragma unroll 4
+            for (int i = 0; i < d; ++i) {
+                const float4 q0 = *reinterpret_cast<const float4*>(qs + swz(i, tg));
+                const float4 q1 = *reinterpret_cast<const float4*>(qs + swz(i, tg + 4));
+                const float sv = Ss[i * 32 + lane];
+                acc2[0] += q0.x * sv; acc2[1] += q0.y * sv; acc2[2] += q0.z * sv; acc2[3] += q0.w * sv;
+                acc2[4] += q1.x * sv; acc2[5] += q1.y * sv; acc2[6] += q1.z * sv; acc2[7] += q1.w * sv;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = tg + j;
+                if (t < n && col_ok) o[((size_t)(tb + t) * H + h) * cols + c0 + lane] = acc[j] + expf((float)Bs[t]) * acc2[j];
+            }
+        }
+        __syncthreads();                          // every read of the old state is done
+        // the state after the chunk: warp wg takes rows wg, wg + 8, ...
+        const double b_end = Bs[n - 1];
+#pragma unroll
+        for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] = s_ < n ? vreg[s_] * expf((float)(b_end - Bs[s_]) + ls[s_]) : 0.f;
+        const float gn = expf((float)b_end);
+        for (int i = wg; i < d; i += kChunkThreads / 32) {
+            float a = 0.f;
+#pragma unroll
+            for (int s4 = 0; s4 < kChunk; s4 += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(ks + swz(i, s4));
+                a += kv.x * vreg[s4] + kv.y * vreg[s4 + 1] + kv.z * vreg[s4 + 2] + kv.w * vreg[s4 + 3];
+            }
+            Ss[i * 32 + lane] = gn * Ss[i * 32 + lane] + a;
+        }
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
+        if (c0 + (x & 31) < cols) S[(size_t)(x >> 5) * cols + c0 + (x & 31)] = Ss[x];
 }
 
 // out[t, h, :] = u / sqrt(mean(u^2) + eps) * w[h * dv + :] * sigmoid(gate[t, h, :]) * out_scale with
@@ -202,6 +358,27 @@ extern "C" int se_memory_scan(const void* proj, int pitch, int q_off, int k_off,
         else SE_MEM_LAUNCH(32);
     });
 #undef SE_MEM_LAUNCH
+    SE_LAUNCH_CHECK();
+}
+
+// The same recurrence in chunks of 64 tokens (closed form per chunk): for steps with prompt portions.
+extern "C" int se_memory_chunk(const void* proj, int pitch, int q_off, int k_off, int v_off, const float* gates,
+                               float q_scale, float* state, long long state_pitch, const int* cu_q, const int* seq_rows,
+                               float* o, int entries, int H, int d, int dv, int dtype, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (d <= 0 || d > se_memory_max_head_dim() || dv <= 0 || H <= 0 || H > 65535 || (dv + 32) / 32 > 65535)
+        return SE_ERR_UNSUPPORTED;
+    dim3 grid(entries, H, (dv + 1 + 31) / 32);
+    const size_t smem = (size_t)(2 * d * se::kPitch + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + se::kChunk) * sizeof(float) +
+                        se::kChunk * sizeof(double);
+    SE_DISPATCH_DTYPE(dtype, T, {
+        cudaError_t e = cudaFuncSetAttribute(se::memory_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(se::memory_chunk_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (e != cudaSuccess) return (int)e;
+        se::memory_chunk_kernel<T><<<grid, se::kChunkThreads, smem, stream>>>((const T*)proj, pitch, q_off, k_off, v_off, gates, q_scale,
+                                                                             state, state_pitch, cu_q, seq_rows, o, H, d, dv);
+    });
     SE_LAUNCH_CHECK();
 }
 

@@ -575,7 +575,7 @@ def delta_out(o, gate, w, out, *, heads: int, v_head_dim: int, eps: float, silu:
 # ---- matrix memory (csrc/matrix_memory.cu) ---------------------------------------------------
 
 def memory_gates(proj, i_off: int, f_off: int, bias, cap: float, state, m_off: int, step, gates, *, heads: int):
-    """The gates of a matrix memory: ``gates[t, h] = (keep, take, exp(-m))`` from the log input and forget
+    """The gates of a matrix memory: ``gates[t, h] = (log keep, log take, exp(-m))`` from the log input and forget
     gates (columns ``i_off + h`` and ``f_off + h`` of the projection, plus ``bias`` [2, heads]), each
     ``cap tanh(. / cap)``; the running maximum ``m`` lives at ``state[row, m_off + h]`` and is brought up to date."""
     _check(_fn("se_memory_gates", "piii" "pf" "pli" "pp" "p" "ii" "ip")(
@@ -594,6 +594,17 @@ def memory_scan(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float,
         float(q_scale), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
         _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim, dtype_code(proj.dtype), _stream()),
         "memory_scan")
+    return o
+
+
+def memory_chunk(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float, state, step, o, *, heads, head_dim,
+                 v_head_dim):
+    """:func:`memory_scan` in chunks of 64 tokens (closed form per chunk): for steps with prompt portions."""
+    _check(_fn("se_memory_chunk", "piiii" "pf" "pl" "pp" "p" "iiii" "ip")(
+        proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(gates, torch.float32, "gates"),
+        float(q_scale), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
+        _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim, dtype_code(proj.dtype), _stream()),
+        "memory_chunk")
     return o
 
 
@@ -1039,17 +1050,15 @@ def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, ma
                     head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None, softcap=None,
                     sink: bool = False, gate=None, keep_first: int = 0):
     """Prompt-portion attention on tcgen05 (head size 128, values of the same size)."""
-    if keep_first:
-        raise ValueError("the tcgen05 prompt kernel keeps no first keys beside a window")
     if int(v_head_dim or head_dim) != head_dim:
         raise ValueError("the tcgen05 prompt kernel takes values of the keys' head size")
-    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ii" "fipi" "p")(
+    _check(_fn("se_attn_prefill_tc", "pppippppp" "iiiiii" "f" "ii" "fipi" "pi" "p")(
         _ptr(q, torch.bfloat16, "q"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(out, torch.bfloat16, "out"), _ptr(error_word(q.device)),
         entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
         cache.shape[0] if num_pages is None else int(num_pages),
-        *_softmax_options(q, gate, num_heads, head_dim, softcap, sink), _stream()),
+        *_softmax_options(q, gate, num_heads, head_dim, softcap, sink, keep_first or 0), _stream()),
         "attn_prefill_tc")
     return out
 

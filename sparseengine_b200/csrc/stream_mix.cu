@@ -19,15 +19,59 @@ namespace se {
 
 constexpr int kMaxStreams = 8;
 
-template <typename T>
+// V columns per thread at a time: 4 (16-byte accesses of the streams) where the width and the addresses allow, else 1.
+template <typename T, int V>
+__device__ __forceinline__ void load_act(const T* p, float* v) {
+    if constexpr (V == 1) {
+        v[0] = to_float(p[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(hh[0]), b = __bfloat1622float2(hh[1]);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_act(T* p, const float* v) {
+    if constexpr (V == 1) {
+        p[0] = from_float<T>(v[0]);
+    } else if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint2 raw;
+        __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&raw);
+        hh[0] = __floats2bfloat162_rn(v[0], v[1]);
+        hh[1] = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+}
+template <int V>
+__device__ __forceinline__ void load_f32(const float* p, float* v) {
+    if constexpr (V == 1) {
+        v[0] = p[0];
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+}
+template <int V>
+__device__ __forceinline__ void store_f32(float* p, const float* v) {
+    if constexpr (V == 1) p[0] = v[0];
+    else *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+template <typename T, int V, int S>
 __global__ void __launch_bounds__(256)
-stream_mix_kernel(float* streams, int S, int width, const T* __restrict__ y, const T* __restrict__ gate,
+stream_mix_kernel(float* streams, int width, const T* __restrict__ y, const T* __restrict__ gate,
                   const float* __restrict__ gate_bias, const float* __restrict__ mix, const float* __restrict__ out_w,
                   const float* __restrict__ in_w, const float* __restrict__ norm_w, float eps, T* __restrict__ h,
                   int store) {
     extern __shared__ __align__(16) float urow[];
     __shared__ float scratch[33];
-    __shared__ float sm_mix[kMaxStreams * kMaxStreams], sm_out[kMaxStreams], sm_in[kMaxStreams];
+    __shared__ float sm_mix[S * S], sm_out[S], sm_in[S];
     const size_t t = blockIdx.x;
     if (threadIdx.x < S * S && y != nullptr) sm_mix[threadIdx.x] = mix[threadIdx.x];
     if (threadIdx.x < S) {
@@ -37,48 +81,62 @@ stream_mix_kernel(float* streams, int S, int width, const T* __restrict__ y, con
     __syncthreads();
     float* base = streams + t * S * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float x[kMaxStreams];
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+        float x[S][V];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) x[s] = s < S ? base[(size_t)s * width + i] : 0.f;
+        for (int s = 0; s < S; ++s) load_f32<V>(base + (size_t)s * width + i, x[s]);
         if (y != nullptr) {
-            float yv = to_float(y[t * width + i]);
+            float yv[V];
+            load_act<T, V>(y + t * width + i, yv);
             if (gate != nullptr) {
-                const float z = to_float(gate[t * width + i]) + (gate_bias != nullptr ? gate_bias[i] : 0.f);
-                yv *= 1.f / (1.f + expf(-z));
-            }
-            float nx[kMaxStreams];
+                float z[V], b[V];
+                load_act<T, V>(gate + t * width + i, z);
+                if (gate_bias != nullptr) {
+                    load_f32<V>(gate_bias + i, b);
 #pragma unroll
-            for (int d = 0; d < kMaxStreams; ++d) {
-                float v = 0.f;
-                if (d < S) {
-#pragma unroll
-                    for (int s = 0; s < kMaxStreams; ++s)
-                        if (s < S) v += sm_mix[s * S + d] * x[s];
-                    v += sm_out[d] * yv;
+                    for (int j = 0; j < V; ++j) z[j] += b[j];
                 }
-                nx[d] = v;
-            }
 #pragma unroll
-            for (int d = 0; d < kMaxStreams; ++d) {
-                x[d] = nx[d];
-                if (d < S && store) base[(size_t)d * width + i] = nx[d];
+                for (int j = 0; j < V; ++j) yv[j] *= 1.f / (1.f + expf(-z[j]));
+            }
+            float nx[S][V];
+#pragma unroll
+            for (int d = 0; d < S; ++d)
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int s = 0; s < S; ++s) v += sm_mix[s * S + d] * x[s][j];
+                    nx[d][j] = v + sm_out[d] * yv[j];
+                }
+#pragma unroll
+            for (int d = 0; d < S; ++d) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) x[d][j] = nx[d][j];
+                if (store) store_f32<V>(base + (size_t)d * width + i, nx[d]);
             }
         }
         if (h != nullptr) {
-            float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
-                if (s < S) u += sm_in[s] * x[s];
-            urow[i] = u;
-            ss += u * u;
+            for (int j = 0; j < V; ++j) {
+                float u = 0.f;
+#pragma unroll
+                for (int s = 0; s < S; ++s) u += sm_in[s] * x[s][j];
+                urow[i + j] = u;
+                ss += u * u;
+            }
         }
     }
     if (h == nullptr) return;
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
     // every thread reads back the elements it wrote itself
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        h[t * width + i] = from_float<T>(urow[i] * inv * norm_w[i]);
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+        float w[V], o[V];
+        load_f32<V>(norm_w + i, w);
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = urow[i + j] * inv * w[j];
+        store_act<T, V>(h + t * width + i, o);
+    }
 }
 
 // streams[t][s] = table[ids[t]] * scale for every s (32-bit product)
@@ -142,15 +200,37 @@ extern "C" int se_stream_mix(float* streams, int tokens, int S, int width, const
     if (h != nullptr && norm_w == nullptr) return SE_ERR_ARGUMENT;
     if (y == nullptr && h == nullptr) return 0;
     const size_t smem = h != nullptr ? (size_t)width * sizeof(float) : 0;
-    const int threads = width >= 1024 ? 256 : 128;
+    auto aligned16 = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = width % 4 == 0 && aligned16(streams) && aligned16(y) && aligned16(gate) && aligned16(gate_bias) &&
+                     aligned16(norm_w) && aligned16(h);
+    const int per = vec ? 4 : 1;
+    const int threads = width / per >= 256 ? 256 : width / per >= 128 ? 128 : 64;
+#define SE_MIX_LAUNCH(V, SN)                                                                                             \
+    {                                                                                                                    \
+        if (smem > 40 * 1024) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(se::stream_mix_kernel<T, V, SN>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 (int)smem);                                                             \
+            if (e != cudaSuccess) return (int)e;                                                                         \
+        }                                                                                                                \
+        se::stream_mix_kernel<T, V, SN><<<tokens, threads, smem, stream>>>(streams, width, (const T*)y, (const T*)gate,  \
+                                                                           gate_bias, mix, out_w, in_w, norm_w, eps, (T*)h, store); \
+    }
+#define SE_MIX_STREAMS(V)                                                                                                \
+    switch (S) {                                                                                                         \
+        case 1: SE_MIX_LAUNCH(V, 1) break;                                                                               \
+        case 2: SE_MIX_LAUNCH(V, 2) break;                                                                               \
+        case 3: SE_MIX_LAUNCH(V, 3) break;                                                                               \
+        case 4: SE_MIX_LAUNCH(V, 4) break;                                                                               \
+        case 5: SE_MIX_LAUNCH(V, 5) break;                                                                               \
+        case 6: SE_MIX_LAUNCH(V, 6) break;                                                                               \
+        case 7: SE_MIX_LAUNCH(V, 7) break;                                                                               \
+        default: SE_MIX_LAUNCH(V, 8) break;                                                                              \
+    }
     SE_DISPATCH_DTYPE(dtype, T, {
-        if (smem > 40 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(se::stream_mix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        se::stream_mix_kernel<T><<<tokens, threads, smem, stream>>>(streams, S, width, (const T*)y, (const T*)gate, gate_bias, mix,
-                                                                    out_w, in_w, norm_w, eps, (T*)h, store);
+        if (vec) { SE_MIX_STREAMS(4) } else { SE_MIX_STREAMS(1) }
     });
+#undef SE_MIX_STREAMS
+#undef SE_MIX_LAUNCH
     SE_LAUNCH_CHECK();
 }
 

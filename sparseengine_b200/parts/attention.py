@@ -215,7 +215,7 @@ class PagedAttention(Mixer):
                                 step_inputs_settled=after_qk_prep, **options)
             else:
                 # prompt portions: tcgen05 + tensor memory for head size 128 (values as wide), m16n8k16 tiles otherwise
-                fn = (ops.attn_prefill_tc if s.value_dim == s.head_dim and s.sink != "learned" and not s.keep_first
+                fn = (ops.attn_prefill_tc if s.value_dim == s.head_dim
                       and ops.attn_prefill_tc_supported(s.head_dim, s.num_heads, s.num_kv_heads) else ops.attn_prefill)
                 fn(q, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, out, entries=step.num_seqs,
                    max_q_len=step.max_q_len, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,

@@ -241,7 +241,7 @@ class MatrixMemoryMixer(Mixer):
         self.i_off = self.g_off + self.vv
         self.f_off = self.i_off + s.num_heads
         self.m_off = s.num_heads * s.head_dim * (s.v_head_dim + 1)
-        self.out_scale = 1.0        # a caller that weighs this mixer's output may fold the weight in here
+    chunk_min_tokens = 16        # the longest entry of a step from which the chunked kernel runs; None: never
 
     def parameters(self):
         s = self.spec
@@ -261,8 +261,12 @@ class MatrixMemoryMixer(Mixer):
         ops.memory_gates(proj, self.i_off, self.f_off, self.gate_bias, s.gate_cap, slot.state, self.m_off, step, gates,
                          heads=s.num_heads)
         o = torch.empty(tokens, s.num_heads, s.v_head_dim + 1, dtype=torch.float32, device=dev)
-        ops.memory_scan(proj, 0, self.qk, 2 * self.qk, gates, s.head_dim ** -0.5, slot.state, step, o, heads=s.num_heads,
-                        head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        # a step with a prompt portion takes the recurrence in chunks of 64 tokens (closed form per chunk);
+        # steps of single tokens and of short pieces walk it token by token
+        chunked = self.chunk_min_tokens is not None and step.max_q_len >= self.chunk_min_tokens
+        (ops.memory_chunk if chunked else ops.memory_scan)(
+            proj, 0, self.qk, 2 * self.qk, gates, s.head_dim ** -0.5, slot.state, step, o, heads=s.num_heads,
+            head_dim=s.head_dim, v_head_dim=s.v_head_dim)
         gated = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
         ops.memory_out(o, gates, proj, self.g_off, self.norm_w, gated, heads=s.num_heads, v_head_dim=s.v_head_dim,
                        eps=s.norm_eps, den_eps=s.den_eps)

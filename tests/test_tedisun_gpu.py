@@ -421,13 +421,19 @@ def test_tensor_core_attention_against_the_plain_kernel(d, dv, heads, kv_heads, 
     split = torch.full_like(plain, float("nan"))
     max_keys = max(kv_lens) if window is None else min(max(kv_lens), window + keep)
     ops.attn_decode(q, cache, table, seq_rows, token_seq, positions, split, max_keys=max_keys, **common)
+    others = [(portions, "portions"), (split, "split keys")]
+    if d == dv and ops.attn_prefill_tc_supported(d, heads, kv_heads):
+        tc = torch.full_like(plain, float("nan"))
+        ops.attn_prefill_tc(q, cache.view(-1, 2, kv_heads, page, d), table, seq_rows, cu_q, kv_len, tc, entries=entries,
+                            max_q_len=max(q_lens), **common)
+        others.append((tc, "portions, tensor memory"))
     ops.error_check(dev)
-    for other, what in ((portions, "portions"), (split, "split keys")):
+    for other, what in others:
         assert bool(torch.isfinite(other.float()).all()), what
         assert float((other.float() - plain.float()).abs().max()) < 3e-2 * float(plain.float().abs().max()), what
 
 
-@pytest.mark.parametrize("heads,d,dv", [(3, 12, 20), (2, 64, 64), (1, 256, 31), (4, 130, 33)])
+@pytest.mark.parametrize("heads,d,dv", [(3, 12, 20), (2, 64, 64), (1, 256, 31), (4, 130, 33), (2, 128, 128)])
 def test_the_matrix_memory_kernels_against_the_recurrence_written_out(heads, d, dv):
     """Gates, recurrence and read-out of the three kernels against the same equations in 64-bit torch, from non-zero
     states and maxima, entries of 1, 31, 32, 33 and 200 tokens in one step; the states they leave."""
@@ -450,13 +456,16 @@ def test_the_matrix_memory_kernels_against_the_recurrence_written_out(heads, d, 
     bias = torch.randn(2 * heads, generator=g, device=dev)
     norm_w = 1.0 + 0.1 * torch.randn(vv, generator=g, device=dev)
     state0 = torch.randn(5, m_off + heads, generator=g, device=dev) * 0.3
-    state = state0.clone()
-    gates = torch.empty(tokens, heads, 3, device=dev)
-    ops.memory_gates(proj, i_off, f_off, bias, cap, state, m_off, step, gates, heads=heads)
-    o = torch.full((tokens, heads, dv + 1), float("nan"), device=dev)
-    ops.memory_scan(proj, 0, qk, 2 * qk, gates, d ** -0.5, state, step, o, heads=heads, head_dim=d, v_head_dim=dv)
-    out = torch.full((tokens, vv), float("nan"), device=dev)
-    ops.memory_out(o, gates, proj, g_off, norm_w, out, heads=heads, v_head_dim=dv, eps=eps, den_eps=1e-6)
+    results = []
+    for walk in (ops.memory_scan, ops.memory_chunk):       # token by token; in chunks of 64 tokens
+        state = state0.clone()
+        gates = torch.empty(tokens, heads, 3, device=dev)
+        ops.memory_gates(proj, i_off, f_off, bias, cap, state, m_off, step, gates, heads=heads)
+        o = torch.full((tokens, heads, dv + 1), float("nan"), device=dev)
+        walk(proj, 0, qk, 2 * qk, gates, d ** -0.5, state, step, o, heads=heads, head_dim=d, v_head_dim=dv)
+        out = torch.full((tokens, vv), float("nan"), device=dev)
+        ops.memory_out(o, gates, proj, g_off, norm_w, out, heads=heads, v_head_dim=dv, eps=eps, den_eps=1e-6)
+        results.append((out, state))
     P, B, Wn = proj.double().cpu(), bias.double().cpu(), norm_w.double().cpu()
     want = torch.zeros(tokens, vv, dtype=torch.float64)
     left = state0.double().cpu().clone()
@@ -478,9 +487,10 @@ def test_the_matrix_memory_kernels_against_the_recurrence_written_out(heads, d, 
             want[t] = u
         left[rows[e], :m_off] = S.reshape(-1)
         left[rows[e], m_off:] = m
-    assert bool(torch.isfinite(out).all())
-    assert float((out.double().cpu() - want).abs().max()) < 5e-5 * float(want.abs().max())
-    assert float((state.double().cpu() - left).abs().max()) < 5e-5 * float(left.abs().max())
+    for out, state in results:
+        assert bool(torch.isfinite(out).all())
+        assert float((out.double().cpu() - want).abs().max()) < 5e-5 * float(want.abs().max())
+        assert float((state.double().cpu() - left).abs().max()) < 5e-5 * float(left.abs().max())
 
 
 # ---- the entry point -----------------------------------------------------------------------------
