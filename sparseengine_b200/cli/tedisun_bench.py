@@ -157,6 +157,10 @@ def _kernels(width: int, cases, pk: dict) -> dict:
         add("memory_scan", lambda: ops.memory_scan(proj_m, 0, qk, 2 * qk, gates, dm ** -0.5, state, step, om, heads=Hm, head_dim=dm,
                                                    v_head_dim=dvm), scan_bytes, iters=5)
         rec["memory_scan"]["us_per_token_of_a_request"] = round(rec["memory_scan"]["us"] / per, 3)
+        if per >= 16:
+            add("memory_chunk", lambda: ops.memory_chunk(proj_m, 0, qk, 2 * qk, gates, dm ** -0.5, state, step, om, heads=Hm, head_dim=dm,
+                                                         v_head_dim=dvm), scan_bytes, iters=5)
+            rec["memory_chunk"]["us_per_token_of_a_request"] = round(rec["memory_chunk"]["us"] / per, 3)
         gm = torch.empty(tokens, vv, device=dev, dtype=bf)
         add("memory_out", lambda: ops.memory_out(om, gates, proj_m, g_off, nwm, gm, heads=Hm, v_head_dim=dvm, eps=1e-6, den_eps=1e-6),
             tokens * vv * 8)

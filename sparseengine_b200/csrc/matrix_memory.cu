@@ -36,14 +36,25 @@ __global__ void memory_gates_kernel(const T* proj, int pitch, int i_off, int f_o
     float* mp = state + (size_t)seq_rows[e] * state_pitch + m_off + h;
     float m_in = *mp;
     const float bi = bias != nullptr ? bias[h] : 0.f, bf = bias != nullptr ? bias[H + h] : 0.f;
+    // the gates' projections of the next 32 tokens are asked for before this round's are used
+    auto fetch = [&](int t, float& a, float& b) {
+        if (t < t1) {
+            const T* row = proj + (size_t)t * pitch;
+            a = to_float(row[i_off + h]);
+            b = to_float(row[f_off + h]);
+        }
+    };
+    float a_next = 0.f, b_next = 0.f;
+    fetch(t0 + lane, a_next, b_next);
     for (int base = t0; base < t1; base += 32) {
         const int t = base + lane;
         const bool valid = t < t1;
+        const float a_now = a_next, b_now = b_next;
+        fetch(base + 32 + lane, a_next, b_next);
         float gi = -INFINITY, gf = 0.f;
         if (valid) {
-            const T* row = proj + (size_t)t * pitch;
-            gi = cap * tanhf((to_float(row[i_off + h]) + bi) / cap);
-            gf = log_sigmoid_f(cap * tanhf((to_float(row[f_off + h]) + bf) / cap));
+            gi = cap * tanhf((a_now + bi) / cap);
+            gf = log_sigmoid_f(cap * tanhf((b_now + bf) / cap));
         }
         float F = gf;                       // sum of the log forget gates up to this token, within the 32
 #pragma unroll
@@ -171,7 +182,8 @@ template <typename T>
 __global__ void __launch_bounds__(kChunkThreads, 2)
 memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, const float* __restrict__ gates,
                     float q_scale, float* state, long long state_pitch, const int* __restrict__ cu_q,
-                    const int* __restrict__ seq_rows, float* __restrict__ o, int H, int d, int dv) {
+                    const int* __restrict__ seq_rows, float* __restrict__ o, int H, int d, int dv, int max_seg, int seg_len,
+                    float* __restrict__ seg_state, double* __restrict__ seg_logs) {
     extern __shared__ __align__(16) float chunk_smem[];
     float* qs = chunk_smem;                      // [d][kPitch]
     float* ks = qs + d * kPitch;                 // [d][kPitch]
@@ -180,41 +192,100 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
     float* Ss = As + kChunk * kChunk;            // [d][32]
     float* ls = Ss + d * 32;                     // [64] log takes
     double* Bs = reinterpret_cast<double*>(ls + kChunk);      // [64] sums of the log keeps (8-byte aligned: every part before is a multiple of 8 bytes)
-    const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    // With segments (seg_state != nullptr) block x = entry * max_seg + segment walks `seg_len` tokens of its entry from
+    // a zero state, leaves the state it ends with in seg_state and the sum of its log keeps in seg_logs; what the true
+    // state at the segment's start adds to the outputs follows in memory_seg_fix_kernel.  Without, it walks the whole
+    // entry from the carried state.
+    const int e = blockIdx.x / max_seg, sg = blockIdx.x - e * max_seg;
+    const int h = blockIdx.y, c0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
     const int cols = dv + 1;
-    const int t_first = cu_q[e], t_last = cu_q[e + 1];
+    const int t_first = seg_state != nullptr ? cu_q[e] + sg * seg_len : cu_q[e];
+    const int t_last = seg_state != nullptr ? min(cu_q[e + 1], t_first + seg_len) : cu_q[e + 1];
     if (t_last <= t_first) return;
-    float* S = state + (size_t)seq_rows[e] * state_pitch + (size_t)h * d * cols;
+    float* S = seg_state != nullptr ? seg_state + (((size_t)e * max_seg + sg) * H + h) * d * cols
+                                    : state + (size_t)seq_rows[e] * state_pitch + (size_t)h * d * cols;
     const bool col_ok = c0 + lane < cols;
     for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
-        Ss[x] = c0 + (x & 31) < cols ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+        Ss[x] = (seg_state == nullptr && c0 + (x & 31) < cols) ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+    double log_total = 0.0;                       // the sum of the log keeps of all chunks so far
+    const bool vec = (d & 7) == 0 && (pitch & 7) == 0 && (q_off & 7) == 0 && (k_off & 7) == 0 && aligned8(proj);
 
     for (int tb = t_first; tb < t_last; tb += kChunk) {
         const int n = min(kChunk, t_last - tb);
         __syncthreads();                          // the chunk before is done with q, k, v and A; the state is up to date
-        for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
-            const int t = x / d, i = x - t * d;
-            float qv = 0.f, kv = 0.f;
-            if (t < n) {
-                const T* row = proj + (size_t)(tb + t) * pitch;
-                qv = to_float(row[q_off + h * d + i]) * q_scale;
-                kv = to_float(row[k_off + h * d + i]);
-            }
-            qs[swz(i, t)] = qv;
-            ks[swz(i, t)] = kv;
-        }
-        for (int x = threadIdx.x; x < kChunk * 32; x += kChunkThreads) {
-            const int t = x >> 5, c = c0 + (x & 31);
-            vs[x] = t < n ? (c < dv ? to_float(proj[(size_t)(tb + t) * pitch + v_off + h * dv + c]) : (c == dv ? 1.f : 0.f)) : 0.f;
-        }
-        if (wg == 0) {                            // the sums of the log keeps, 64-bit, by one warp
-            double carry = 0.0;
+        // Everything the chunk needs from memory is asked for before any of it is used (one trip to memory per
+        // chunk, not one per kind of input): the gates by warp 0, the values, then q and k.
+        float g_keep[2] = {0.f, 0.f}, g_take[2] = {-INFINITY, -INFINITY};
+        if (wg == 0) {
+#pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int t = half * 32 + lane;
-                const float* g = gates + ((size_t)(tb + t) * H + h) * 3;
-                double b = t < n ? (double)g[0] : 0.0;
-                ls[t] = t < n ? g[1] : -INFINITY;
+                if (t < n) {
+                    const float* g = gates + ((size_t)(tb + t) * H + h) * 3;
+                    g_keep[half] = g[0];
+                    g_take[half] = g[1];
+                }
+            }
+        }
+        float vv[kChunk * 32 / kChunkThreads];
+#pragma unroll
+        for (int r = 0; r < kChunk * 32 / kChunkThreads; ++r) {
+            const int x = threadIdx.x + r * kChunkThreads, t = x >> 5, c = c0 + (x & 31);
+            vv[r] = t < n ? (c < dv ? to_float(proj[(size_t)(tb + t) * pitch + v_off + h * dv + c]) : (c == dv ? 1.f : 0.f)) : 0.f;
+        }
+        if (vec) {
+            // eight elements a load; a warp's lanes take the same eight dims of 32 tokens in a row, so that the
+            // transposing stores fall into 32 banks
+            const int pieces = kChunk * (d >> 3);
+            for (int base = threadIdx.x; base < pieces; base += 4 * kChunkThreads) {
+                float qv[4][8], kv[4][8];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int x = base + r * kChunkThreads, t = x & (kChunk - 1), i = (x >> 6) * 8;
+                    if (x < pieces && t < n) {
+                        const T* row = proj + (size_t)(tb + t) * pitch + h * d + i;
+                        load8(row + q_off, qv[r]);
+                        load8(row + k_off, kv[r]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) qv[r][j] = kv[r][j] = 0.f;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int x = base + r * kChunkThreads, t = x & (kChunk - 1), i = (x >> 6) * 8;
+                    if (x < pieces) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            qs[swz(i + j, t)] = qv[r][j] * q_scale;
+                            ks[swz(i + j, t)] = kv[r][j];
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
+                const int t = x / d, i = x - t * d;
+                float qv = 0.f, kv = 0.f;
+                if (t < n) {
+                    const T* row = proj + (size_t)(tb + t) * pitch;
+                    qv = to_float(row[q_off + h * d + i]) * q_scale;
+                    kv = to_float(row[k_off + h * d + i]);
+                }
+                qs[swz(i, t)] = qv;
+                ks[swz(i, t)] = kv;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kChunk * 32 / kChunkThreads; ++r) vs[threadIdx.x + r * kChunkThreads] = vv[r];
+        if (wg == 0) {                            // the sums of the log keeps, 64-bit, by one warp
+            double carry = 0.0;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int t = half * 32 + lane;
+                double b = (double)g_keep[half];
+                ls[t] = g_take[half];
 #pragma unroll
                 for (int off = 1; off < 32; off <<= 1) {
                     const double v = __shfl_up_sync(0xffffffffu, b, off);
@@ -285,6 +356,7 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
         __syncthreads();                          // every read of the old state is done
         // the state after the chunk: warp wg takes rows wg, wg + 8, ...
         const double b_end = Bs[n - 1];
+        log_total += b_end;
 #pragma unroll
         for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] = s_ < n ? vreg[s_] * expf((float)(b_end - Bs[s_]) + ls[s_]) : 0.f;
         const float gn = expf((float)b_end);
@@ -301,6 +373,107 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
     __syncthreads();
     for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
         if (c0 + (x & 31) < cols) S[(size_t)(x >> 5) * cols + c0 + (x & 31)] = Ss[x];
+    if (seg_logs != nullptr && threadIdx.x == 0 && blockIdx.z == 0) seg_logs[((size_t)e * max_seg + sg) * H + h] = log_total;
+}
+
+// The segments of an entry joined: seg_state[e, j] holds what segment j alone leaves; it becomes the state at
+// segment j's start, S_0 = the carried state, S_(j+1) = exp(sum of segment j's log keeps) S_j + (what segment j
+// leaves), and the last one goes back to the entry's state row.  One thread per state element.
+__global__ void memory_seg_join_kernel(float* __restrict__ seg_state, const double* __restrict__ seg_logs, float* state,
+                                       long long state_pitch, const int* __restrict__ cu_q, const int* __restrict__ seq_rows,
+                                       int H, int d, int cols, int max_seg, int seg_len) {
+    const int e = blockIdx.y, h = blockIdx.z;
+    const int n = cu_q[e + 1] - cu_q[e];
+    if (n <= 0) return;
+    const int nseg = (n + seg_len - 1) / seg_len;
+    float* S = state + (size_t)seq_rows[e] * state_pitch + (size_t)h * d * cols;
+    for (int x = blockIdx.x * blockDim.x + threadIdx.x; x < d * cols; x += gridDim.x * blockDim.x) {
+        float cur = S[x];
+        for (int j = 0; j < nseg; ++j) {
+            float* p = seg_state + (((size_t)e * max_seg + j) * H + h) * d * cols + x;
+            const float left = *p;
+            *p = cur;
+            cur = expf((float)seg_logs[((size_t)e * max_seg + j) * H + h]) * cur + left;
+        }
+        S[x] = cur;
+    }
+}
+
+// o_t += exp(B_t) S_start^T q_t for the tokens of a segment (B_t: the sum of the log keeps from the segment's start
+// to t): what the state at the segment's start adds to outputs that were computed from a zero state.
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads, 2)
+memory_seg_fix_kernel(const T* proj, int pitch, int q_off, const float* __restrict__ gates, float q_scale,
+                      const float* __restrict__ seg_state, const int* __restrict__ cu_q, float* __restrict__ o, int H, int d,
+                      int dv, int max_seg, int seg_len) {
+    extern __shared__ __align__(16) float fix_smem[];
+    float* qs = fix_smem;                        // [d][kPitch]
+    float* Ss = qs + d * kPitch;                 // [d][32]
+    double* Bs = reinterpret_cast<double*>(Ss + d * 32);      // [64]
+    const int e = blockIdx.x / max_seg, sg = blockIdx.x - e * max_seg;
+    const int h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
+    const int cols = dv + 1;
+    const int t_first = cu_q[e] + sg * seg_len, t_last = min(cu_q[e + 1], t_first + seg_len);
+    if (t_last <= t_first) return;
+    const float* S = seg_state + (((size_t)e * max_seg + sg) * H + h) * d * cols;
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
+        Ss[x] = c0 + (x & 31) < cols ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+    const bool col_ok = c0 + lane < cols;
+    const bool vec = (d & 7) == 0 && (pitch & 7) == 0 && (q_off & 7) == 0 && aligned8(proj);
+    double base_log = 0.0;                        // the sum of the log keeps of the segment's earlier chunks (warp 0 keeps it)
+    for (int tb = t_first; tb < t_last; tb += kChunk) {
+        const int n = min(kChunk, t_last - tb);
+        __syncthreads();
+        if (vec) {
+            const int pieces = kChunk * (d >> 3);
+            for (int x = threadIdx.x; x < pieces; x += kChunkThreads) {
+                const int t = x & (kChunk - 1), i = (x >> 6) * 8;
+                float qv[8] = {};
+                if (t < n) load8(proj + (size_t)(tb + t) * pitch + q_off + h * d + i, qv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) qs[swz(i + j, t)] = qv[j] * q_scale;
+            }
+        } else {
+            for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
+                const int t = x / d, i = x - t * d;
+                qs[swz(i, t)] = t < n ? to_float(proj[(size_t)(tb + t) * pitch + q_off + h * d + i]) * q_scale : 0.f;
+            }
+        }
+        if (wg == 0) {
+            double carry = base_log;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int t = half * 32 + lane;
+                double b = t < n ? (double)gates[((size_t)(tb + t) * H + h) * 3] : 0.0;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const double v = __shfl_up_sync(0xffffffffu, b, off);
+                    if (lane >= off) b += v;
+                }
+                b += carry;
+                Bs[t] = b;
+                carry = __shfl_sync(0xffffffffu, b, 31);
+            }
+            base_log = carry;
+        }
+        __syncthreads();
+        const int tg = wg * 8;
+        float acc2[8] = {};
+#pragma unroll 4
+        for (int i = 0; i < d; ++i) {
+            const float4 q0 = *reinterpret_cast<const float4*>(qs + swz(i, tg));
+            const float4 q1 = *reinterpret_cast<const float4*>(qs + swz(i, tg + 4));
+            const float sv = Ss[i * 32 + lane];
+            acc2[0] += q0.x * sv; acc2[1] += q0.y * sv; acc2[2] += q0.z * sv; acc2[3] += q0.w * sv;
+            acc2[4] += q1.x * sv; acc2[5] += q1.y * sv; acc2[6] += q1.z * sv; acc2[7] += q1.w * sv;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int t = tg + j;
+            if (t < n && col_ok) o[((size_t)(tb + t) * H + h) * cols + c0 + lane] += expf((float)Bs[t]) * acc2[j];
+        }
+    }
 }
 
 // out[t, h, :] = u / sqrt(mean(u^2) + eps) * w[h * dv + :] * sigmoid(gate[t, h, :]) * out_scale with
@@ -364,20 +537,39 @@ extern "C" int se_memory_scan(const void* proj, int pitch, int q_off, int k_off,
 // The same recurrence in chunks of 64 tokens (closed form per chunk): for steps with prompt portions.
 extern "C" int se_memory_chunk(const void* proj, int pitch, int q_off, int k_off, int v_off, const float* gates,
                                float q_scale, float* state, long long state_pitch, const int* cu_q, const int* seq_rows,
-                               float* o, int entries, int H, int d, int dv, int dtype, cudaStream_t stream) {
+                               float* o, int entries, int H, int d, int dv, int max_seg, int seg_len, float* seg_state,
+                               double* seg_logs, int dtype, cudaStream_t stream) {
+    // max_seg > 1: the entries' tokens in segments of seg_len (a multiple of 64) that run side by side, joined by
+    // the sums of their log keeps (three launches); seg_state: float [entries, max_seg, H, d, dv + 1], seg_logs:
+    // double [entries, max_seg, H].
     if (entries <= 0) return 0;
     if (d <= 0 || d > se_memory_max_head_dim() || dv <= 0 || H <= 0 || H > 65535 || (dv + 32) / 32 > 65535)
         return SE_ERR_UNSUPPORTED;
-    dim3 grid(entries, H, (dv + 1 + 31) / 32);
+    if (max_seg < 1 || (max_seg > 1 && (seg_state == nullptr || seg_logs == nullptr || seg_len <= 0 || seg_len % se::kChunk)))
+        return SE_ERR_ARGUMENT;
+    if ((long long)entries * max_seg > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
+    const bool segments = max_seg > 1;
+    dim3 grid(entries * max_seg, H, (dv + 1 + 31) / 32);
     const size_t smem = (size_t)(2 * d * se::kPitch + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + se::kChunk) * sizeof(float) +
                         se::kChunk * sizeof(double);
+    const size_t fix_smem = (size_t)(d * se::kPitch + d * 32) * sizeof(float) + se::kChunk * sizeof(double);
     SE_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e = cudaFuncSetAttribute(se::memory_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(se::memory_chunk_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) return (int)e;
-        se::memory_chunk_kernel<T><<<grid, se::kChunkThreads, smem, stream>>>((const T*)proj, pitch, q_off, k_off, v_off, gates, q_scale,
-                                                                             state, state_pitch, cu_q, seq_rows, o, H, d, dv);
+        se::memory_chunk_kernel<T><<<grid, se::kChunkThreads, smem, stream>>>(
+            (const T*)proj, pitch, q_off, k_off, v_off, gates, q_scale, state, state_pitch, cu_q, seq_rows, o, H, d, dv, max_seg,
+            segments ? seg_len : 0, segments ? seg_state : nullptr, segments ? seg_logs : nullptr);
+        if (segments) {
+            const int per = d * (dv + 1);
+            se::memory_seg_join_kernel<<<dim3((per + 255) / 256 < 64 ? (per + 255) / 256 : 64, entries, H), 256, 0, stream>>>(
+                seg_state, seg_logs, state, state_pitch, cu_q, seq_rows, H, d, dv + 1, max_seg, seg_len);
+            e = cudaFuncSetAttribute(se::memory_seg_fix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fix_smem);
+            if (e != cudaSuccess) return (int)e;
+            se::memory_seg_fix_kernel<T><<<grid, se::kChunkThreads, fix_smem, stream>>>(
+                (const T*)proj, pitch, q_off, gates, q_scale, seg_state, cu_q, o, H, d, dv, max_seg, seg_len);
+        }
     });
     SE_LAUNCH_CHECK();
 }

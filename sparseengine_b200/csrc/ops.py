@@ -598,13 +598,24 @@ def memory_scan(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float,
 
 
 def memory_chunk(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float, state, step, o, *, heads, head_dim,
-                 v_head_dim):
-    """:func:`memory_scan` in chunks of 64 tokens (closed form per chunk): for steps with prompt portions."""
-    _check(_fn("se_memory_chunk", "piiii" "pf" "pl" "pp" "p" "iiii" "ip")(
+                 v_head_dim, segments=None):
+    """:func:`memory_scan` in chunks of 64 tokens (closed form per chunk): for steps with prompt portions.
+    ``segments``: ``(per entry, tokens each)``, default by :func:`retention_segment_plan` (a single long prompt
+    runs in segments side by side, joined by the sums of their log keeps)."""
+    global launch_count
+    max_seg, seg_len = segments if segments is not None else retention_segment_plan(
+        step.num_seqs, heads, v_head_dim + 1, step.max_q_len, sm_count(proj.device))
+    seg_state = seg_logs = None
+    if max_seg > 1:
+        seg_state = torch.empty(step.num_seqs * max_seg * heads * head_dim * (v_head_dim + 1), dtype=torch.float32,
+                                device=proj.device)
+        seg_logs = torch.empty(step.num_seqs * max_seg * heads, dtype=torch.float64, device=proj.device)
+        launch_count += 2
+    _check(_fn("se_memory_chunk", "piiii" "pf" "pl" "pp" "p" "iiii" "iipp" "ip")(
         proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(gates, torch.float32, "gates"),
         float(q_scale), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
-        _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim, dtype_code(proj.dtype), _stream()),
-        "memory_chunk")
+        _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim, int(max_seg), int(seg_len),
+        _ptr(seg_state), _ptr(seg_logs), dtype_code(proj.dtype), _stream()), "memory_chunk")
     return o
 
 

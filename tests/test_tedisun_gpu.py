@@ -457,12 +457,14 @@ def test_the_matrix_memory_kernels_against_the_recurrence_written_out(heads, d, 
     norm_w = 1.0 + 0.1 * torch.randn(vv, generator=g, device=dev)
     state0 = torch.randn(5, m_off + heads, generator=g, device=dev) * 0.3
     results = []
-    for walk in (ops.memory_scan, ops.memory_chunk):       # token by token; in chunks of 64 tokens
+    # token by token; in chunks of 64 tokens, in one pass and in segments of 64 and of 128 tokens side by side
+    for walk, kw in ((ops.memory_scan, {}), (ops.memory_chunk, {"segments": (1, 0)}), (ops.memory_chunk, {"segments": (4, 64)}),
+                     (ops.memory_chunk, {"segments": (2, 128)})):
         state = state0.clone()
         gates = torch.empty(tokens, heads, 3, device=dev)
         ops.memory_gates(proj, i_off, f_off, bias, cap, state, m_off, step, gates, heads=heads)
         o = torch.full((tokens, heads, dv + 1), float("nan"), device=dev)
-        walk(proj, 0, qk, 2 * qk, gates, d ** -0.5, state, step, o, heads=heads, head_dim=d, v_head_dim=dv)
+        walk(proj, 0, qk, 2 * qk, gates, d ** -0.5, state, step, o, heads=heads, head_dim=d, v_head_dim=dv, **kw)
         out = torch.full((tokens, vv), float("nan"), device=dev)
         ops.memory_out(o, gates, proj, g_off, norm_w, out, heads=heads, v_head_dim=dv, eps=eps, den_eps=1e-6)
         results.append((out, state))
