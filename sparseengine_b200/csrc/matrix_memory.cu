@@ -169,9 +169,10 @@ memory_scan_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, co
 //     S_new = exp(B_(n-1)) S_0 + sum_s exp(B_(n-1) - B_s + l_s) k_s [v_s | 1]^T
 //
 // which is three small matrix products per chunk instead of a chain of n dependent steps; every exponent
-// is at most 0 (the running maximum sees to that).  All of it is 32-bit FMA arithmetic; the sums B are taken
+// is at most 0 (the running maximum sees to that).  The normaliser's column of ones needs no products: its share of
+// o_t is the sum over s of the weighted scores, which the block of a head's first 32 value columns adds up.  All of it is 32-bit FMA arithmetic; the sums B are taken
 // in 64-bit, so that their differences keep the digits of the single terms.  One block per (entry, head,
-// 32 columns of [values | 1]): q and k of the chunk lie transposed in shared memory (`[dim][token]`, padded
+// 32 value columns): q and k of the chunk lie transposed in shared memory (`[dim][token]`, padded
 // rows), the block's slice of the state stays in shared memory over all chunks.
 constexpr int kChunk = 64;
 constexpr int kChunkThreads = 256;
@@ -192,6 +193,8 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
     float* Ss = As + kChunk * kChunk;            // [d][32]
     float* ls = Ss + d * 32;                     // [64] log takes
     double* Bs = reinterpret_cast<double*>(ls + kChunk);      // [64] sums of the log keeps (8-byte aligned: every part before is a multiple of 8 bytes)
+    float* ws = reinterpret_cast<float*>(Bs + kChunk);        // [64] what token s adds to the state after the chunk: exp(B_(n-1) - B_s + l_s)
+    float* Ns = ws + kChunk;                                  // [d] the normaliser n (the state's last column), kept by the block of the first columns
     // With segments (seg_state != nullptr) block x = entry * max_seg + segment walks `seg_len` tokens of its entry from
     // a zero state, leaves the state it ends with in seg_state and the sum of its log keeps in seg_logs; what the true
     // state at the segment's start adds to the outputs follows in memory_seg_fix_kernel.  Without, it walks the whole
@@ -205,9 +208,14 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
     if (t_last <= t_first) return;
     float* S = seg_state != nullptr ? seg_state + (((size_t)e * max_seg + sg) * H + h) * d * cols
                                     : state + (size_t)seq_rows[e] * state_pitch + (size_t)h * d * cols;
-    const bool col_ok = c0 + lane < cols;
+    const bool col_ok = c0 + lane < dv;
+    // the block of a head's first 32 value columns also keeps the normaliser: its "value column" is all ones, so its
+    // share of an output is the sum of the chunk's weighted scores, and no block spends a column's work on it
+    const bool has_n = blockIdx.z == 0;
     for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
-        Ss[x] = (seg_state == nullptr && c0 + (x & 31) < cols) ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+        Ss[x] = (seg_state == nullptr && c0 + (x & 31) < dv) ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+    if (has_n)
+        for (int i = threadIdx.x; i < d; i += kChunkThreads) Ns[i] = seg_state == nullptr ? S[(size_t)i * cols + dv] : 0.f;
     double log_total = 0.0;                       // the sum of the log keeps of all chunks so far
     const bool vec = (d & 7) == 0 && (pitch & 7) == 0 && (q_off & 7) == 0 && (k_off & 7) == 0 && aligned8(proj);
 
@@ -232,7 +240,7 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
 #pragma unroll
         for (int r = 0; r < kChunk * 32 / kChunkThreads; ++r) {
             const int x = threadIdx.x + r * kChunkThreads, t = x >> 5, c = c0 + (x & 31);
-            vv[r] = t < n ? (c < dv ? to_float(proj[(size_t)(tb + t) * pitch + v_off + h * dv + c]) : (c == dv ? 1.f : 0.f)) : 0.f;
+            vv[r] = (t < n && c < dv) ? to_float(proj[(size_t)(tb + t) * pitch + v_off + h * dv + c]) : 0.f;
         }
         if (vec) {
             // eight elements a load; a warp's lanes take the same eight dims of 32 tokens in a row, so that the
@@ -353,13 +361,35 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
                 if (t < n && col_ok) o[((size_t)(tb + t) * H + h) * cols + c0 + lane] = acc[j] + expf((float)Bs[t]) * acc2[j];
             }
         }
-        __syncthreads();                          // every read of the old state is done
-        // the state after the chunk: warp wg takes rows wg, wg + 8, ...
         const double b_end = Bs[n - 1];
         log_total += b_end;
+        if (threadIdx.x < kChunk) {
+            const int t = threadIdx.x;
+            if (has_n) {                          // n . q of token t: the column of ones
+                float den = 0.f, dot = 0.f;
+#pragma unroll 8
+                for (int s_ = 0; s_ < kChunk; ++s_) den += As[s_ * kChunk + t];
+#pragma unroll 4
+                for (int i = 0; i < d; ++i) dot += qs[swz(i, t)] * Ns[i];
+                if (t < n) o[((size_t)(tb + t) * H + h) * cols + dv] = den + expf((float)Bs[t]) * dot;
+            }
+            ws[t] = t < n ? expf((float)(b_end - Bs[t]) + ls[t]) : 0.f;
+        }
+        __syncthreads();                          // every read of the old state is done
+        // the state after the chunk: warp wg takes rows wg, wg + 8, ...
 #pragma unroll
-        for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] = s_ < n ? vreg[s_] * expf((float)(b_end - Bs[s_]) + ls[s_]) : 0.f;
+        for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] *= ws[s_];
         const float gn = expf((float)b_end);
+        if (has_n)
+            for (int i = threadIdx.x; i < d; i += kChunkThreads) {
+                float a = 0.f;
+#pragma unroll
+                for (int s4 = 0; s4 < kChunk; s4 += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(ks + swz(i, s4));
+                    a += kv.x * ws[s4] + kv.y * ws[s4 + 1] + kv.z * ws[s4 + 2] + kv.w * ws[s4 + 3];
+                }
+                Ns[i] = gn * Ns[i] + a;
+            }
         for (int i = wg; i < d; i += kChunkThreads / 32) {
             float a = 0.f;
 #pragma unroll
@@ -372,7 +402,9 @@ memory_chunk_kernel(const T* proj, int pitch, int q_off, int k_off, int v_off, c
     }
     __syncthreads();
     for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
-        if (c0 + (x & 31) < cols) S[(size_t)(x >> 5) * cols + c0 + (x & 31)] = Ss[x];
+        if (c0 + (x & 31) < dv) S[(size_t)(x >> 5) * cols + c0 + (x & 31)] = Ss[x];
+    if (has_n)
+        for (int i = threadIdx.x; i < d; i += kChunkThreads) S[(size_t)i * cols + dv] = Ns[i];
     if (seg_logs != nullptr && threadIdx.x == 0 && blockIdx.z == 0) seg_logs[((size_t)e * max_seg + sg) * H + h] = log_total;
 }
 
@@ -410,6 +442,7 @@ memory_seg_fix_kernel(const T* proj, int pitch, int q_off, const float* __restri
     float* qs = fix_smem;                        // [d][kPitch]
     float* Ss = qs + d * kPitch;                 // [d][32]
     double* Bs = reinterpret_cast<double*>(Ss + d * 32);      // [64]
+    float* Ns = reinterpret_cast<float*>(Bs + kChunk);        // [d] the normaliser at the segment's start (block of the first columns)
     const int e = blockIdx.x / max_seg, sg = blockIdx.x - e * max_seg;
     const int h = blockIdx.y, c0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
@@ -418,8 +451,11 @@ memory_seg_fix_kernel(const T* proj, int pitch, int q_off, const float* __restri
     if (t_last <= t_first) return;
     const float* S = seg_state + (((size_t)e * max_seg + sg) * H + h) * d * cols;
     for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
-        Ss[x] = c0 + (x & 31) < cols ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
-    const bool col_ok = c0 + lane < cols;
+        Ss[x] = c0 + (x & 31) < dv ? S[(size_t)(x >> 5) * cols + c0 + (x & 31)] : 0.f;
+    const bool has_n = blockIdx.z == 0;
+    if (has_n)
+        for (int i = threadIdx.x; i < d; i += kChunkThreads) Ns[i] = S[(size_t)i * cols + dv];
+    const bool col_ok = c0 + lane < dv;
     const bool vec = (d & 7) == 0 && (pitch & 7) == 0 && (q_off & 7) == 0 && aligned8(proj);
     double base_log = 0.0;                        // the sum of the log keeps of the segment's earlier chunks (warp 0 keeps it)
     for (int tb = t_first; tb < t_last; tb += kChunk) {
@@ -472,6 +508,13 @@ memory_seg_fix_kernel(const T* proj, int pitch, int q_off, const float* __restri
         for (int j = 0; j < 8; ++j) {
             const int t = tg + j;
             if (t < n && col_ok) o[((size_t)(tb + t) * H + h) * cols + c0 + lane] += expf((float)Bs[t]) * acc2[j];
+        }
+        if (has_n && threadIdx.x < n) {
+            const int t = threadIdx.x;
+            float dot = 0.f;
+#pragma unroll 4
+            for (int i = 0; i < d; ++i) dot += qs[swz(i, t)] * Ns[i];
+            o[((size_t)(tb + t) * H + h) * cols + dv] += expf((float)Bs[t]) * dot;
         }
     }
 }
@@ -549,10 +592,10 @@ extern "C" int se_memory_chunk(const void* proj, int pitch, int q_off, int k_off
         return SE_ERR_ARGUMENT;
     if ((long long)entries * max_seg > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
     const bool segments = max_seg > 1;
-    dim3 grid(entries * max_seg, H, (dv + 1 + 31) / 32);
-    const size_t smem = (size_t)(2 * d * se::kPitch + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + se::kChunk) * sizeof(float) +
+    dim3 grid(entries * max_seg, H, (dv + 31) / 32);
+    const size_t smem = (size_t)(2 * d * se::kPitch + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + 2 * se::kChunk + d) * sizeof(float) +
                         se::kChunk * sizeof(double);
-    const size_t fix_smem = (size_t)(d * se::kPitch + d * 32) * sizeof(float) + se::kChunk * sizeof(double);
+    const size_t fix_smem = (size_t)(d * se::kPitch + d * 32 + d) * sizeof(float) + se::kChunk * sizeof(double);
     SE_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e = cudaFuncSetAttribute(se::memory_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;

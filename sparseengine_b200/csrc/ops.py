@@ -49,7 +49,7 @@ LIMITS = {
     "recurrent_max_state_rows": 512,        # rows of a recurrence's state on the key/state side (16 registers x 32 lanes)
     "latent_max_row": 1024,                 # latent plus shared key part of one position (32 registers x 32 lanes)
     "retention_max_head_dim": 256,          # rows of a retention state (32 registers x 8 warps)
-    "stream_mix_max_streams": 8,            # a column's stream values live in registers
+    "stream_mix_max_streams": 16,           # a column's stream values live in registers
     "memory_max_head_dim": 256,             # rows of a matrix memory's state (32 registers x 8 warps)
     "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
 }
@@ -604,7 +604,7 @@ def memory_chunk(proj, q_off: int, k_off: int, v_off: int, gates, q_scale: float
     runs in segments side by side, joined by the sums of their log keeps)."""
     global launch_count
     max_seg, seg_len = segments if segments is not None else retention_segment_plan(
-        step.num_seqs, heads, v_head_dim + 1, step.max_q_len, sm_count(proj.device))
+        step.num_seqs, heads, v_head_dim, step.max_q_len, sm_count(proj.device))
     seg_state = seg_logs = None
     if max_seg > 1:
         seg_state = torch.empty(step.num_seqs * max_seg * heads * head_dim * (v_head_dim + 1), dtype=torch.float32,

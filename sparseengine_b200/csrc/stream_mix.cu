@@ -17,7 +17,7 @@
 
 namespace se {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;      // up to 8 with four columns per thread, beyond that one column per thread
 
 // V columns per thread at a time: 4 (16-byte accesses of the streams) where the width and the addresses allow, else 1.
 template <typename T, int V>
@@ -201,7 +201,7 @@ extern "C" int se_stream_mix(float* streams, int tokens, int S, int width, const
     if (y == nullptr && h == nullptr) return 0;
     const size_t smem = h != nullptr ? (size_t)width * sizeof(float) : 0;
     auto aligned16 = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-    const bool vec = width % 4 == 0 && aligned16(streams) && aligned16(y) && aligned16(gate) && aligned16(gate_bias) &&
+    const bool vec = S <= 8 && width % 4 == 0 && aligned16(streams) && aligned16(y) && aligned16(gate) && aligned16(gate_bias) &&
                      aligned16(norm_w) && aligned16(h);
     const int per = vec ? 4 : 1;
     const int threads = width / per >= 256 ? 256 : width / per >= 128 ? 128 : 64;
@@ -226,9 +226,21 @@ extern "C" int se_stream_mix(float* streams, int tokens, int S, int width, const
         case 7: SE_MIX_LAUNCH(V, 7) break;                                                                               \
         default: SE_MIX_LAUNCH(V, 8) break;                                                                              \
     }
+#define SE_MIX_MANY()                                                                                                    \
+    switch (S) {                                                                                                         \
+        case 9: SE_MIX_LAUNCH(1, 9) break;                                                                               \
+        case 10: SE_MIX_LAUNCH(1, 10) break;                                                                             \
+        case 11: SE_MIX_LAUNCH(1, 11) break;                                                                             \
+        case 12: SE_MIX_LAUNCH(1, 12) break;                                                                             \
+        case 13: SE_MIX_LAUNCH(1, 13) break;                                                                             \
+        case 14: SE_MIX_LAUNCH(1, 14) break;                                                                             \
+        case 15: SE_MIX_LAUNCH(1, 15) break;                                                                             \
+        default: SE_MIX_LAUNCH(1, 16) break;                                                                             \
+    }
     SE_DISPATCH_DTYPE(dtype, T, {
-        if (vec) { SE_MIX_STREAMS(4) } else { SE_MIX_STREAMS(1) }
+        if (S > 8) { SE_MIX_MANY() } else if (vec) { SE_MIX_STREAMS(4) } else { SE_MIX_STREAMS(1) }
     });
+#undef SE_MIX_MANY
 #undef SE_MIX_STREAMS
 #undef SE_MIX_LAUNCH
     SE_LAUNCH_CHECK();

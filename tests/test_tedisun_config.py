@@ -116,7 +116,7 @@ def test_what_a_configuration_must_have():
         breaker(c)
         with pytest.raises(ValueError, match=word):
             load_model_spec(c)
-    for breaker, word in ((lambda c: c.__setitem__("streams", 9), "residual streams"),
+    for breaker, word in ((lambda c: c.__setitem__("streams", 17), "residual streams"),
                           (lambda c: c["layers"][1]["mixer"]["left"]["mask"].__setitem__("keep_first", -1), "keep_first"),
                           (lambda c: c["layers"][1]["mixer"]["right"].__setitem__("dim", 300), "head_dim"),
                           (lambda c: c["layers"][0]["mlp"]["router"].__setitem__("top", 9), "top_k")):

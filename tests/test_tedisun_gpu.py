@@ -179,13 +179,18 @@ SINGLE = {
     "identity_experts": dict(layers=[delta(1, 1, 4, 4, 2, mlp=moe(3, 3, 16, 3))]),
     "one_plain_stream": dict(layers=[delta(2, 1, 8, 8, 3, mlp=moe(4, 2, 16, 1))], streams=None),
     "eight_streams": dict(layers=[delta(2, 1, 8, 8, 3, mlp=moe(4, 2, 16, 1))], streams=8),
+    "eleven_streams": dict(layers=[delta(2, 1, 8, 8, 3, mlp=moe(4, 2, 16, 1))], streams=11),
+    "delta_rule_one_tap": dict(layers=[delta(2, 2, 8, 8, 1)]),
+    "a_width_that_is_no_multiple_of_four": dict(layers=[delta(2, 1, 8, 8, 3, mlp=moe(4, 2, 10, 1)),
+                                                        par(att(2, 1, 8, 8, 7, 1, rot=8), mem(2, 8, 8), mlp=moe(3, 2, 6, 2))], width=54),
 }
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("which", sorted(SINGLE))
 def test_each_mechanism_alone(tmp_path, which, dtype):
-    cfg = config(40, 50, **SINGLE[which])
+    kw = dict(SINGLE[which])
+    cfg = config(kw.pop("width", 40), 50, **kw)
     w = write_folder(str(tmp_path), cfg, 5)
     seqs = prompts(cfg, (37, 1, 18), 3)
     for cut in (tu.trace_whole, lambda s: tu.trace_chunks(s, sizes=(2, 3, 1, 5, 2)), lambda s: tu.trace_tail_decode(s, tail=9)):
