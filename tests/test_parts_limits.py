@@ -21,7 +21,8 @@ def test_attention_sizes():
     make_mixer(AttentionSpec(**ok), torch.float32)
     for change, words in ((dict(head_dim=24), "head_dim"), (dict(head_dim=272), "head_dim"),
                           (dict(num_heads=5), "multiple"), (dict(num_heads=70000, num_kv_heads=1), "65535"),
-                          (dict(window=0), "window"), (dict(qk_norm="per_head"), "qk_norm"),
+                          (dict(window=0), "window"), (dict(qk_norm="per_token"), "qk_norm"),
+                          (dict(qk_norm="per_head"), "per-head norms need prep='general'"),
                           (dict(position=RotarySpec(rotary_dim=32)), "rotates 32")):
         with pytest.raises(ValueError, match=words):
             make_mixer(AttentionSpec(**dict(ok, **change)), torch.float32)
