@@ -36,7 +36,7 @@ __global__ void memory_gates_kernel(const T* proj, int pitch, int i_off, int f_o
     float* mp = state + (size_t)seq_rows[e] * state_pitch + m_off + h;
     float m_in = *mp;
     const float bi = bias != nullptr ? bias[h] : 0.f, bf = bias != nullptr ? bias[H + h] : 0.f;
-    // the gates' projections of the next 32 tokens are asked for before this round's are used
+    // the gates' projections of the next 32 tokens are asked for before the current 32 are used
     auto fetch = [&](int t, float& a, float& b) {
         if (t < t1) {
             const T* row = proj + (size_t)t * pitch;
