@@ -50,7 +50,8 @@ LIMITS = {
     "latent_max_row": 1024,                 # latent plus shared key part of one position (32 registers x 32 lanes)
     "retention_max_head_dim": 256,          # rows of a retention state (32 registers x 8 warps)
     "stream_mix_max_streams": 16,           # a column's stream values live in registers
-    "memory_max_head_dim": 256,             # rows of a matrix memory's state (32 registers x 8 warps)
+    "memory_max_head_dim": 256,
+    "delta_chunk_max_head_dim": 256,        # a chunk's transposed q and k tiles in shared memory             # rows of a matrix memory's state (32 registers x 8 warps)
     "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
 }
 
@@ -540,16 +541,17 @@ def gated_group_norm(y, proj, z_off: int, w, out, *, parts: int, eps: float):
 
 
 def delta_prep(qkv, a, proj, b_off: int, dt_bias, a_log, dec, beta, *, heads, kv_heads, head_dim, v_head_dim,
-               unit_eps: float, q_scale: float, per_head: bool = False):
+               unit_eps: float, q_scale: float, per_head: bool = False, log_dec=None):
     """``a``: the decay projection, ``[tokens, heads * head_dim]`` or (``per_head``) ``[tokens, heads]``; it may
-    be a view of columns of the input projection (rows ``a.stride(0)`` apart)."""
+    be a view of columns of the input projection (rows ``a.stride(0)`` apart).  ``log_dec`` (with ``per_head``):
+    receives the decays' logarithms ``[tokens, heads]``, which the chunked recurrence reads."""
     if a.dtype != proj.dtype or a.stride(-1) != 1:
         raise TypeError("delta_prep: the decay projection must have the projection's type and unit column stride")
-    _check(_fn("se_delta_prep", "ppipii" "pp" "pp" "iiiii" "ff" "iip")(
+    _check(_fn("se_delta_prep", "ppipii" "pp" "pp" "iiiii" "ff" "ipip")(
         _ptr(qkv, torch.float32, "qkv"), a.data_ptr(), a.stride(0), proj.data_ptr(), proj.stride(0), int(b_off),
         _ptr(dt_bias, torch.float32), _ptr(a_log, torch.float32), _ptr(dec, torch.float32), _ptr(beta, torch.float32),
         qkv.shape[0], heads, kv_heads, head_dim, v_head_dim, float(unit_eps), float(q_scale), int(per_head),
-        dtype_code(proj.dtype), _stream()), "delta_prep")
+        _ptr(log_dec, torch.float32, "log_dec"), dtype_code(proj.dtype), _stream()), "delta_prep")
 
 
 def delta_scan(qkv, dec, beta, state, step, o, *, heads, kv_heads, head_dim, v_head_dim):
@@ -557,6 +559,16 @@ def delta_scan(qkv, dec, beta, state, step, o, *, heads, kv_heads, head_dim, v_h
         _ptr(qkv, torch.float32, "qkv"), _ptr(dec, torch.float32), _ptr(beta, torch.float32),
         _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
         _ptr(o, torch.float32, "o"), step.num_seqs, heads, kv_heads, head_dim, v_head_dim, _stream()), "delta_scan")
+    return o
+
+
+def delta_chunk(qkv, log_dec, beta, state, step, o, *, heads, kv_heads, head_dim, v_head_dim):
+    """The delta rule with one decay per head in chunks of 64 tokens (a triangular system per chunk, then three small
+    matrix products; csrc/delta_chunk.cu): for steps with prompt portions.  ``log_dec`` [tokens, heads]: log decays."""
+    _check(_fn("se_delta_chunk", "ppp" "pl" "pp" "p" "iiiii" "p")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(log_dec, torch.float32, "log_dec"), _ptr(beta, torch.float32, "beta"),
+        _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
+        _ptr(o, torch.float32, "o"), step.num_seqs, heads, kv_heads, head_dim, v_head_dim, _stream()), "delta_chunk")
     return o
 
 

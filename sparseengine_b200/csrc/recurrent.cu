@@ -630,7 +630,7 @@ template <typename T>
 __global__ void delta_prep_kernel(float* qkv, int width, const T* a, int a_pitch, const T* proj, int pitch, int b_off,
                                   const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                   float* __restrict__ dec, float* __restrict__ beta, int H, int G, int d,
-                                  float unit_eps, float q_scale, int per_head) {
+                                  float unit_eps, float q_scale, int per_head, float* __restrict__ log_dec) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     float* row = qkv + (size_t)t * width;
     for (int hh = warp; hh < 2 * G; hh += warps) {          // q heads, then k heads
@@ -646,8 +646,12 @@ __global__ void delta_prep_kernel(float* qkv, int width, const T* a, int a_pitch
         const float rate = expf(a_log[h]);
         dec[(size_t)t * H * d + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * a_pitch + j]) + dt_bias[j]));
     }
-    for (int h = threadIdx.x; h < H; h += blockDim.x)
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
         beta[(size_t)t * H + h] = sigmoid_f(to_float(proj[(size_t)t * pitch + b_off + h]));
+        // the decays' logarithms (one per head), for the chunked form of the recurrence
+        if (log_dec != nullptr)
+            log_dec[(size_t)t * H + h] = -expf(a_log[h]) * softplus_f(to_float(a[(size_t)t * a_pitch + h]) + dt_bias[h]);
+    }
 }
 
 // ---- epilogues ---------------------------------------------------------------------------------
@@ -788,13 +792,15 @@ extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt
 
 extern "C" int se_delta_prep(float* qkv, const void* a, int a_pitch, const void* proj, int pitch, int b_off,
                              const float* dt_bias, const float* a_log, float* dec, float* beta, int tokens, int H, int G,
-                             int d, int dv, float unit_eps, float q_scale, int per_head, int dtype, cudaStream_t stream) {
+                             int d, int dv, float unit_eps, float q_scale, int per_head, float* log_dec, int dtype,
+                             cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || a_pitch < (per_head ? H : H * d)) return SE_ERR_ARGUMENT;
+    if (log_dec != nullptr && !per_head) return SE_ERR_ARGUMENT;
     SE_DISPATCH_DTYPE(dtype, T,
         se::delta_prep_kernel<T><<<tokens, 256, 0, stream>>>(qkv, 2 * G * d + H * dv, (const T*)a, a_pitch, (const T*)proj, pitch,
                                                             b_off, dt_bias, a_log, dec, beta, H, G, d, unit_eps, q_scale,
-                                                            per_head));
+                                                            per_head, log_dec));
     SE_LAUNCH_CHECK();
 }
 

@@ -86,6 +86,7 @@ class GatedDeltaMixer(Mixer):
     with ``a`` a column of the input projection, and the gate ``gate_activation(g)`` with ``g`` columns of
     the input projection (no low ranks)."""
     graph_safe = True
+    chunk_min_tokens = 16        # (one decay per head) the longest entry of a step from which the chunked kernel runs; None: never
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -139,12 +140,20 @@ class GatedDeltaMixer(Mixer):
             a, gate = linear(a, self.a2), linear(gate, self.g2)
         dec = torch.empty(tokens, s.num_heads * s.head_dim, dtype=torch.float32, device=dev)
         beta = torch.empty(tokens, s.num_heads, dtype=torch.float32, device=dev)
+        # one decay per head: a step with a prompt portion takes the recurrence in chunks of 64 tokens
+        chunked = (self.per_head and self.chunk_min_tokens is not None and step.max_q_len >= self.chunk_min_tokens
+                   and s.head_dim <= ops.LIMITS["delta_chunk_max_head_dim"])
+        log_dec = torch.empty(tokens, s.num_heads, dtype=torch.float32, device=dev) if chunked else None
         ops.delta_prep(qkv, a, proj, self.b_off, self.dt_bias, self.a_log, dec, beta, heads=s.num_heads,
                        kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim, unit_eps=s.unit_eps,
-                       q_scale=s.head_dim ** -0.5, per_head=self.per_head)
+                       q_scale=s.head_dim ** -0.5, per_head=self.per_head, log_dec=log_dec)
         o = torch.empty(tokens, self.vv, dtype=torch.float32, device=dev)
-        ops.delta_scan(qkv, dec, beta, slot.state, step, o, heads=s.num_heads, kv_heads=s.num_kv_heads,
-                       head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        if chunked:
+            ops.delta_chunk(qkv, log_dec, beta, slot.state, step, o, heads=s.num_heads, kv_heads=s.num_kv_heads,
+                            head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        else:
+            ops.delta_scan(qkv, dec, beta, slot.state, step, o, heads=s.num_heads, kv_heads=s.num_kv_heads,
+                           head_dim=s.head_dim, v_head_dim=s.v_head_dim)
         out = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
         ops.delta_out(o, gate, self.norm_w, out, heads=s.num_heads, v_head_dim=s.v_head_dim, eps=s.norm_eps,
                       silu=s.gate_activation == "silu")

@@ -553,3 +553,43 @@ def test_command_line(folders, tmp_path):
                             *extra], cwd=tu.ROOT, capture_output=True, text=True, timeout=300)
         assert r.returncode == 0, r.stderr[-2000:]
         assert r.stdout.strip()
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,dv", [(3, 1, 12, 20), (2, 2, 64, 64), (1, 1, 256, 31), (4, 2, 130, 33), (4, 2, 128, 128)])
+def test_the_chunked_delta_rule_against_the_walk_token_by_token(heads, kv_heads, d, dv):
+    """The triangular system per chunk of 64 tokens and the chain of single steps, on the same inputs and from the
+    same non-zero states: entries of 1, 63, 64, 65 and 200 tokens in one step, decays from almost 1 down to 0.3, writes of
+    every strength; outputs and the states they leave."""
+    from types import SimpleNamespace
+    from sparseengine_b200.csrc import ops
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(d + dv)
+    q_lens = [63, 1, 200, 64, 65]
+    tokens, entries = sum(q_lens), len(q_lens)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    step = SimpleNamespace(cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), num_seqs=entries, max_q_len=max(q_lens),
+                           seq_rows=torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32, device=dev))
+    qk, vv = kv_heads * d, heads * dv
+    qkv = torch.randn(tokens, 2 * qk + vv, generator=g, device=dev)
+    unit = qkv[:, :2 * qk].view(tokens, 2 * kv_heads, d)
+    unit /= unit.norm(dim=-1, keepdim=True)
+    unit[:, :kv_heads] *= d ** -0.5
+    log_dec = -torch.rand(tokens, heads, generator=g, device=dev) ** 3 * 1.2
+    beta = torch.rand(tokens, heads, generator=g, device=dev)
+    dec = log_dec.exp().repeat_interleave(d, 1).contiguous()
+    state0 = torch.randn(5, heads * d * dv + 7, generator=g, device=dev) * 0.2
+    outs = []
+    for chunked in (False, True):
+        state = state0.clone()
+        o = torch.full((tokens, vv), float("nan"), device=dev)
+        if chunked:
+            ops.delta_chunk(qkv, log_dec, beta, state, step, o, heads=heads, kv_heads=kv_heads, head_dim=d, v_head_dim=dv)
+        else:
+            ops.delta_scan(qkv, dec, beta, state, step, o, heads=heads, kv_heads=kv_heads, head_dim=d, v_head_dim=dv)
+        outs.append((o, state))
+    (o1, s1), (o2, s2) = outs
+    assert bool(torch.isfinite(o2).all())
+    assert float((o1 - o2).abs().max()) < 3e-5 * float(o1.abs().max())
+    assert float((s1 - s2).abs().max()) < 3e-5 * float(s1.abs().max())
