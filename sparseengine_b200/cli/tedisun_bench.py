@@ -193,6 +193,11 @@ def _kernels(width: int, cases, pk: dict) -> dict:
         add("delta_scan", lambda: ops.delta_scan(qkv, dec, beta, state_d, step, o_d, heads=Hd, kv_heads=Gd, head_dim=dd, v_head_dim=dvd),
             tokens * (C + Hd * dd + Hd * dvd) * 4 + entries * Hd * dd * dvd * 8, iters=5)
         rec["delta_scan"]["us_per_token_of_a_request"] = round(rec["delta_scan"]["us"] / per, 3)
+        if per >= 16:
+            log_dec = torch.rand(tokens, Hd, device=dev) * -0.1
+            add("delta_chunk", lambda: ops.delta_chunk(qkv, log_dec, beta, state_d, step, o_d, heads=Hd, kv_heads=Gd, head_dim=dd,
+                                                       v_head_dim=dvd), tokens * (C + Hd + Hd * dvd) * 4 + entries * Hd * dd * dvd * 8, iters=5)
+            rec["delta_chunk"]["us_per_token_of_a_request"] = round(rec["delta_chunk"]["us"] / per, 3)
         out_d = torch.empty(tokens, Hd * dvd, device=dev, dtype=bf)
         add("delta_out (silu gate from the projection)", lambda: ops.delta_out(
             o_d, proj_d[:, C + 2 * Hd:], nwd, out_d, heads=Hd, v_head_dim=dvd, eps=1e-6, silu=True), tokens * Hd * dvd * 8)

@@ -140,9 +140,14 @@ class GatedDeltaMixer(Mixer):
             a, gate = linear(a, self.a2), linear(gate, self.g2)
         dec = torch.empty(tokens, s.num_heads * s.head_dim, dtype=torch.float32, device=dev)
         beta = torch.empty(tokens, s.num_heads, dtype=torch.float32, device=dev)
-        # one decay per head: a step with a prompt portion takes the recurrence in chunks of 64 tokens
+        # One decay per head: a step with a prompt portion whose (entry, head, 32 columns) blocks do not fill the device
+        # takes the recurrence in chunks of 64 tokens.  The chunked form does about twice the 32-bit multiply-adds of the
+        # walk token by token (the keys' products with one another, the triangular system, the products with the state at
+        # the chunk's start), so it is ahead only while the walk leaves SMs idle (measured at 16 heads of 128 x 128: one
+        # 2,048-token prompt 930 against 1,010 us; four of them about 1,500 against 1,220 us).
         chunked = (self.per_head and self.chunk_min_tokens is not None and step.max_q_len >= self.chunk_min_tokens
-                   and s.head_dim <= ops.LIMITS["delta_chunk_max_head_dim"])
+                   and s.head_dim <= ops.LIMITS["delta_chunk_max_head_dim"]
+                   and step.num_seqs * s.num_heads * (-(-s.v_head_dim // 32)) <= ops.sm_count(dev))
         log_dec = torch.empty(tokens, s.num_heads, dtype=torch.float32, device=dev) if chunked else None
         ops.delta_prep(qkv, a, proj, self.b_off, self.dt_bias, self.a_log, dec, beta, heads=s.num_heads,
                        kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim, unit_eps=s.unit_eps,
