@@ -238,6 +238,7 @@ class MatrixMemoryMixer(Mixer):
     one 32-bit row per request: ``[heads, head_dim, v_head_dim + 1]`` (the normaliser is the last column),
     then the maximum per head."""
     graph_safe = True
+    chunk_min_tokens = 16        # the longest entry of a step from which the chunked kernel runs; None: never
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -255,7 +256,6 @@ class MatrixMemoryMixer(Mixer):
         self.i_off = self.g_off + self.vv
         self.f_off = self.i_off + s.num_heads
         self.m_off = s.num_heads * s.head_dim * (s.v_head_dim + 1)
-    chunk_min_tokens = 16        # the longest entry of a step from which the chunked kernel runs; None: never
 
     def parameters(self):
         s = self.spec

@@ -923,7 +923,8 @@ def test_size_limits_the_parts_check_are_the_launchers_own():
     limit the kernel runs, one past it the launcher says so."""
     from sparseengine_b200.csrc import ops
     for name in ("rmsnorm_max_width", "router_max_experts", "router_max_unaligned_width", "moe_max_experts",
-                 "layernorm_max_width", "recurrent_max_state_rows", "latent_max_row", "retention_max_head_dim"):
+                 "layernorm_max_width", "recurrent_max_state_rows", "latent_max_row", "retention_max_head_dim",
+                 "stream_mix_max_streams", "memory_max_head_dim", "delta_chunk_max_head_dim"):
         assert ops.limit(name) == ops.LIMITS[name], name
     w = ops.LIMITS["rmsnorm_max_width"]
     x, wt = rnd(2, w + 8, seed=1), torch.ones(w + 8, device=DEV)
