@@ -7,8 +7,9 @@ written before attention reads the cache.
 
 The general preparation (``prep="general"``) adds, each by a field of the spec: values of a head
 size of their own, a query temperature, layers without keys of their own, a cap on the scores,
-a sink of score 0 in the softmax, an output gate, and values blended with those of an earlier
-layer.  The blended values are what is cached; the earlier layer's values of this step's tokens
+a sink of score 0 or of a learned score per head in the softmax, an output gate, values blended with
+those of an earlier layer, norms per head, biases on the projections, and first positions that stay
+visible beside a window.  The blended values are what is cached; the earlier layer's values of this step's tokens
 travel from layer to layer in the step's scratch (``StepContext.extras``), so nothing of them
 is kept between steps.
 """
