@@ -37,6 +37,9 @@ class PagedAttention(Mixer):
         if s.prep not in ("rotary", "general"):
             raise ValueError(f"attention prep {s.prep!r} is not known ('rotary' or 'general')")
         self.general = s.prep == "general"
+        # the parameter that projects the mixer's input (a mixer of mixers may stack it with its neighbours' and
+        # hand `forward` the product's columns as `proj`); the rotary preparation reads a matrix of its own
+        self.input_projection = "qkv" if self.general else None
         if self.general:
             # no rotation; any head sizes the plain kernels take
             if not (0 < s.head_dim <= ops.LIMITS["attention_max_head_dim"]
@@ -114,12 +117,14 @@ class PagedAttention(Mixer):
 
     VALUE_MIX_KEY = "attention.value_mix.first"     # in StepContext.extras: the kept values [tokens, kv heads * value_dim]
 
-    def forward_general(self, x, step, slot):
+    def forward_general(self, x, step, slot, proj=None):
         """Whole-projection norms, rotation, query temperature, value blending and the page writes in
-        one kernel (32-bit, rounded once); a layer without keys of its own only prepares its queries."""
+        one kernel (32-bit, rounded once); a layer without keys of its own only prepares its queries.
+        ``proj``: the input's projection if the caller has computed it (a view with a row pitch)."""
         s = self.spec
         tokens = x.shape[0]
-        proj = linear(x, self.qkv)
+        if proj is None:
+            proj = linear(x, self.qkv)
         q_cols, kv_cols = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         v_cols = s.num_kv_heads * s.value_dim
         inv_freq, rotary_dim = None, 0
@@ -157,9 +162,11 @@ class PagedAttention(Mixer):
             y += self.o_bias.to(y.dtype) if y.dtype != torch.float32 else self.o_bias
         return y
 
-    def forward(self, x, step, slot):
+    def forward(self, x, step, slot, proj=None):
         if self.general:
-            return self.forward_general(x, step, slot)
+            return self.forward_general(x, step, slot, proj)
+        if proj is not None:
+            raise ValueError("a projection computed by the caller needs prep='general'")
         s = self.spec
         tokens = x.shape[0]
         # the position part first: whatever it launches to make its table then lies before the

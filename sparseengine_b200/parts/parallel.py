@@ -4,7 +4,10 @@ they return (``config.specs.ParallelMixerSpec``).
 A branch is any registered mixer.  The cache manager sees one mixer: the pages are the branch's that
 asks for pages, the state slot the branch's that asks for one (at most one each).  A branch that
 has a bias on its output projection leaves it to the sum (one kernel: csrc/stream_mix.cu,
-``scaled_sum``), where it is weighed like the branch.
+``scaled_sum``), where it is weighed like the branch.  Branches that name the parameter that
+projects their input (``input_projection``) get one product for all of them: their matrices are
+stacked (the branches' own parameters become views of the stack) and each branch is handed its
+columns of the result.
 """
 from __future__ import annotations
 
@@ -12,6 +15,7 @@ import torch
 
 from ..csrc import ops
 from .base import Mixer, make_mixer, register_mixer
+from .linear import linear
 
 
 class ParallelMixer(Mixer):
@@ -31,6 +35,7 @@ class ParallelMixer(Mixer):
             if hasattr(b, "defer_output_bias"):
                 b.defer_output_bias = True
         self._bias = None
+        self._stacked = None         # the branches' input projections as one matrix, and where each one's rows start
 
     def parameters(self):
         return {f"{name}_{k}": p for name, b in zip(self.spec.names, self.branches) for k, p in b.parameters().items()}
@@ -44,6 +49,19 @@ class ParallelMixer(Mixer):
             bias = b.output_bias() if hasattr(b, "output_bias") else None
             if bias is not None:
                 self._bias = a * bias.float() if self._bias is None else self._bias + a * bias.float()
+        # one product for the branches' input projections
+        self._stacked = None
+        names = [getattr(b, "input_projection", None) for b in self.branches]
+        if all(n is not None and getattr(b, n, None) is not None for n, b in zip(names, self.branches)):
+            parts = [getattr(b, n) for n, b in zip(names, self.branches)]
+            if all(p.dim() == 2 and p.shape[1] == parts[0].shape[1] and p.dtype == parts[0].dtype for p in parts):
+                stack = torch.cat(parts, 0)
+                starts, at = [], 0
+                for n, b, p in zip(names, self.branches, parts):
+                    setattr(b, n, stack[at:at + p.shape[0]])       # the branch's own parameter: a view of the stack
+                    starts.append((at, p.shape[0]))
+                    at += p.shape[0]
+                self._stacked = (stack, starts)
 
     def kv_request(self):
         return next((r for r in (b.kv_request() for b in self.branches) if r is not None), None)
@@ -52,8 +70,13 @@ class ParallelMixer(Mixer):
         return next((r for r in (b.state_request() for b in self.branches) if r is not None), None)
 
     def forward(self, x, step, slot):
-        y0 = self.branches[0].forward(x, step, slot)
-        y1 = self.branches[1].forward(x, step, slot)
+        if self._stacked is not None:
+            stack, starts = self._stacked
+            proj = linear(x, stack)
+            y0, y1 = (b.forward(x, step, slot, proj=proj[:, at:at + n]) for b, (at, n) in zip(self.branches, starts))
+        else:
+            y0 = self.branches[0].forward(x, step, slot)
+            y1 = self.branches[1].forward(x, step, slot)
         return ops.scaled_sum(y0, y1, self.scales[0], self.scales[1], torch.empty_like(y0), bias=self._bias)
 
 

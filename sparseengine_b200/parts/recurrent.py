@@ -267,10 +267,15 @@ class MatrixMemoryMixer(Mixer):
     def state_request(self):
         return StateRequest((self.m_off + self.spec.num_heads,), torch.float32)
 
-    def forward(self, x, step, slot):
+    # the parameter that projects the mixer's input (a mixer of mixers may stack it with its neighbours' and
+    # hand `forward` the product's columns as `proj`)
+    input_projection = "in_proj"
+
+    def forward(self, x, step, slot, proj=None):
         s = self.spec
         tokens, dev = x.shape[0], x.device
-        proj = linear(x, self.in_proj)
+        if proj is None:
+            proj = linear(x, self.in_proj)
         gates = torch.empty(tokens, s.num_heads, 3, dtype=torch.float32, device=dev)
         ops.memory_gates(proj, self.i_off, self.f_off, self.gate_bias, s.gate_cap, slot.state, self.m_off, step, gates,
                          heads=s.num_heads)
